@@ -1,0 +1,91 @@
+/*
+ * opencnn_b200 - C ABI of the B200-native Winograd F(2x2,3x3) convolution operator.
+ *
+ * One shared library is built per output-staging variant, selected at build time exactly as in
+ * the reference (Makefile:3,8): -DBASE, -DOPTSTS64 (default), -DOPTSTS64_CMP, -DOPTLDS64 give
+ * libopencnn_b200_<VARIANT>.so.  All variants compute identical values.
+ *
+ * Tensor layouts (fp32, dense): input CHWN, filter CRSK, output KHWN, workspace [C][4][4][K]
+ * (src/openCNN_winograd.cu:147-153,185; src/FX_m2.cu:58-59,84).  Constraints: N % 32 == 0,
+ * K % 64 == 0, C % 8 == 0, 3x3 filter, stride 1, pad 1, m = 2 (src/config.hpp:19-21).  Unlike
+ * the reference, violations are reported (cudaErrorInvalidValue) instead of computing garbage,
+ * and rectangular images (in_h != in_w) are accepted.
+ *
+ * Return values are cudaError_t codes passed as int, so the header needs no CUDA include.
+ * All pointers are device pointers unless a function says otherwise.  Calls are asynchronous
+ * with respect to the host unless a function says otherwise.
+ */
+#ifndef OPENCNN_B200_H
+#define OPENCNN_B200_H
+
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Opaque: a cudaStream_t. */
+typedef void *opencnn_stream_t;
+
+/* Arithmetic of the batched GEMM.  FP32 is the FFMA path that reproduces the reference bit for
+ * bit; TF32 and BF16 run the GEMM on the tensor cores (operands rounded, fp32 accumulate). */
+enum opencnn_precision { OPENCNN_FP32 = 0, OPENCNN_TF32 = 1, OPENCNN_BF16 = 2 };
+
+/* Replaces convolutionForward_32x64x8 (src/convolutionForward_32x64x8.cu:264-284 and its
+ * _baseline / ampere copies): filter transform into Ww, then the fused kernel, both enqueued on
+ * the legacy default stream; returns the launch status without synchronising.  Same argument
+ * list and meaning: k input, w filter, C output, Ww workspace of at least in_c*16*filt_k
+ * floats, tiles_dim = ceil(in_w/2), tile_size = alpha = 4, m = 2; n (element count) is unused. */
+int convolutionForward_32x64x8(float *k, int in_h, int in_w, float *w, int out_h, int out_w, int out_n,
+                               int out_c, float *C, float *Ww, const unsigned int n, int tiles_dim,
+                               int in_n, int tile_size, int in_c, int filt_k, int filt_c, int filt_h,
+                               int filt_w, int alpha, int m);
+
+/* Replaces convolutionForward (src/openCNN_winograd.cu:204-219), the dispatcher that the
+ * reference's caller uses (src/openCNN_winograd.cu:429-440).  elems_dim is unused there too. */
+int convolutionForward(float *k, int in_h, int in_w, float *w, int out_h, int out_w, int out_n, int out_c,
+                       float *C, float *Ww, const unsigned int n, int tiles_dim, int in_n, int tile_size,
+                       int elems_dim, int in_c, int filt_k, int filt_c, int filt_h, int filt_w, int alpha,
+                       int m);
+
+/* Same operator on a caller-chosen stream and arithmetic.  The reference has only the default
+ * stream (src/convolutionForward_32x64x8.cu:274,281) and only fp32. */
+int opencnn_convolutionForward_stream(const float *input, const float *filter, float *output,
+                                      float *workspace, int in_n, int in_c, int in_h, int in_w, int filt_k,
+                                      int precision, opencnn_stream_t stream);
+
+/* The two halves of the operator on their own.  opencnn_filter_transform replaces the launch of
+ * FX (src/convolutionForward_32x64x8.cu:274); opencnn_winograd_forward replaces the launch of
+ * Winograd_kernel (:281) and expects the workspace that the former wrote.  Callers with fixed
+ * weights can transform once and reuse the workspace. */
+int opencnn_filter_transform(const float *filter, float *workspace, int in_c, int filt_k,
+                             opencnn_stream_t stream);
+int opencnn_winograd_forward(const float *input, const float *workspace, float *output, int in_n, int in_c,
+                             int in_h, int in_w, int filt_k, int precision, opencnn_stream_t stream);
+
+/* Bytes of workspace the operator needs: in_c*16*filt_k floats, as allocated by the reference's
+ * caller (src/openCNN_winograd.cu:309-311). */
+size_t opencnn_workspace_bytes(int in_c, int filt_k);
+
+/* "BASE", "OPTSTS64", "OPTSTS64_CMP" or "OPTLDS64": the -D the library was built with
+ * (src/convolutionForward_32x64x8.cu:18-27, src/config.hpp:28-34). */
+const char *opencnn_variant_name(void);
+
+/* Synchronises the current device and returns the device-side status word: 0 = ok, 1 = a
+ * bounded wait inside a kernel ran out (results are invalid).  Resets the word to 0.  The
+ * reference has no counterpart: its kernels contain no waits. */
+int opencnn_last_device_status(void);
+
+/* Host-buffer front end, the shape of the reference's main() around the operator
+ * (src/openCNN_winograd.cu:300-316 allocation, :470-472 copy back): a plan owns device buffers
+ * for one problem size; run copies input and filter host->device, runs the operator, copies the
+ * output device->host and synchronises.  Host pointers; pinned memory makes the copies
+ * asynchronous but is not required. */
+int opencnn_host_plan_create(void **plan, int in_n, int in_c, int in_h, int in_w, int filt_k, int precision);
+int opencnn_host_plan_run(void *plan, const float *input_host, const float *filter_host, float *output_host);
+int opencnn_host_plan_destroy(void *plan);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* OPENCNN_B200_H */

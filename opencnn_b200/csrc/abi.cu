@@ -1,0 +1,279 @@
+// C ABI of the library (declared in include/opencnn_b200.h): argument validation, TMA
+// descriptors, launches.  Host side of the operator that replaces the reference's
+// convolutionForward (src/openCNN_winograd.cu:204-219) and convolutionForward_32x64x8
+// (src/convolutionForward_32x64x8.cu:264-284).
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cstdint>
+#include <cstdio>
+#include <mutex>
+#include <new>
+
+#include "../../include/opencnn_b200.h"
+#include "fx.cuh"
+#include "wino_fp32.cuh"
+
+#if defined(BASE)
+#define OCB_VARIANT ocb::kBase
+#define OCB_VARIANT_NAME "BASE"
+#elif defined(OPTSTS64_CMP)
+#define OCB_VARIANT ocb::kOptSts64Cmp
+#define OCB_VARIANT_NAME "OPTSTS64_CMP"
+#elif defined(OPTLDS64)
+#define OCB_VARIANT ocb::kOptLds64
+#define OCB_VARIANT_NAME "OPTLDS64"
+#else
+#define OCB_VARIANT ocb::kOptSts64
+#define OCB_VARIANT_NAME "OPTSTS64"
+#endif
+
+namespace {
+
+__device__ int g_status = 0;
+
+constexpr int kMaxDevices = 64;
+
+struct DeviceState {
+  std::once_flag once;
+  cudaError_t init_error = cudaSuccess;
+  int sm_count = 0;
+  int *status_ptr = nullptr;
+};
+DeviceState g_dev[kMaxDevices];
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *,
+                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode = nullptr;
+std::once_flag g_encode_once;
+
+EncodeTiledFn encode_fn() {
+  std::call_once(g_encode_once, [] {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+  });
+  return g_encode;
+}
+
+// Per-device set-up: SM count, the opt-in to large dynamic shared memory, the address of the
+// status word.  Runs once per device, with that device current.
+cudaError_t device_state(DeviceState **out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  DeviceState &st = g_dev[dev];
+  std::call_once(st.once, [&] {
+    cudaError_t err = cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (err == cudaSuccess)
+      err = cudaFuncSetAttribute(ocb::wino_fp32_kernel<OCB_VARIANT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)ocb::SmemLayout<OCB_VARIANT>::kBytes);
+    if (err == cudaSuccess) err = cudaGetSymbolAddress(reinterpret_cast<void **>(&st.status_ptr), g_status);
+    st.init_error = err;
+  });
+  *out = &st;
+  return st.init_error;
+}
+
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+cudaError_t check_shape(int N, int C, int H, int W, int K) {
+  if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || K <= 0) return cudaErrorInvalidValue;
+  if (N % ocb::kBN || K % ocb::kBK || C % ocb::kBC) return cudaErrorInvalidValue;
+  // 32-bit tile arithmetic and TMA extents
+  if ((long long)N * C * H * W >= (1ll << 40) || (long long)N * K * H * W >= (1ll << 40)) return cudaErrorInvalidValue;
+  return cudaSuccess;
+}
+
+cudaError_t launch_fx(const float *filter, float *workspace, int C, int K, cudaStream_t stream) {
+  const int k4 = K / 4;
+  const int total = C * k4;
+  ocb::fx_kernel<<<(total + 127) / 128, 128, 0, stream>>>(reinterpret_cast<const float4 *>(filter),
+                                                        reinterpret_cast<float4 *>(workspace), C, k4);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_wino_fp32(const float *input, const float *workspace, float *output, int N, int C, int H,
+                             int W, int K, cudaStream_t stream) {
+  DeviceState *st = nullptr;
+  cudaError_t e = device_state(&st);
+  if (e != cudaSuccess) return e;
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return cudaErrorNotSupported;
+
+  CUtensorMap tm_in, tm_u;
+  {
+    cuuint64_t dims[4] = {(cuuint64_t)N, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)C};
+    cuuint64_t strides[3] = {(cuuint64_t)N * 4, (cuuint64_t)W * N * 4, (cuuint64_t)H * W * N * 4};
+    cuuint32_t box[4] = {(cuuint32_t)ocb::kBN, 4, 4, (cuuint32_t)ocb::kBC};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    if (enc(&tm_in, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(input), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return cudaErrorInvalidValue;
+  }
+  {
+    cuuint64_t dims[3] = {(cuuint64_t)K, 16, (cuuint64_t)C};
+    cuuint64_t strides[2] = {(cuuint64_t)K * 4, (cuuint64_t)K * 16 * 4};
+    cuuint32_t box[3] = {(cuuint32_t)ocb::kBK, 16, (cuuint32_t)ocb::kBC};
+    cuuint32_t estr[3] = {1, 1, 1};
+    if (enc(&tm_u, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<float *>(workspace), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return cudaErrorInvalidValue;
+  }
+
+  ocb::WinoParams p;
+  p.y = output;
+  p.N = N; p.C = C; p.K = K; p.H = H; p.W = W;
+  p.tiles_h = (H + 1) / 2;
+  p.tiles_w = (W + 1) / 2;
+  p.n_blocks = N / ocb::kBN;
+  p.k_blocks = K / ocb::kBK;
+  const long long tiles = (long long)p.tiles_h * p.tiles_w * p.n_blocks * p.k_blocks;
+  if (tiles > 0x7fffffffll / 8) return cudaErrorInvalidValue;
+  p.total_tiles = (int)tiles;
+  p.chunks_per_tile = C / ocb::kBC;
+  p.status = st->status_ptr;
+  const int grid = p.total_tiles < st->sm_count ? p.total_tiles : st->sm_count;
+  ocb::wino_fp32_kernel<OCB_VARIANT><<<grid, ocb::kThreads, ocb::SmemLayout<OCB_VARIANT>::kBytes, stream>>>(tm_in, tm_u, p);
+  return cudaGetLastError();
+}
+
+cudaError_t forward(const float *input, const float *filter, float *output, float *workspace, int N, int C, int H,
+                    int W, int K, int precision, cudaStream_t stream) {
+  if (!input || !filter || !output || !workspace) return cudaErrorInvalidValue;
+  if (!aligned16(input) || !aligned16(filter) || !aligned16(output) || !aligned16(workspace)) return cudaErrorInvalidValue;
+  cudaError_t e = check_shape(N, C, H, W, K);
+  if (e != cudaSuccess) return e;
+  if (precision != OPENCNN_FP32) return cudaErrorNotSupported;
+  e = launch_fx(filter, workspace, C, K, stream);
+  if (e != cudaSuccess) return e;
+  return launch_wino_fp32(input, workspace, output, N, C, H, W, K, stream);
+}
+
+struct HostPlan {
+  int N, C, H, W, K, precision;
+  float *d_in = nullptr, *d_filt = nullptr, *d_out = nullptr, *d_ws = nullptr;
+  cudaStream_t stream = nullptr;
+};
+
+}  // namespace
+
+extern "C" {
+
+int convolutionForward_32x64x8(float *k, int in_h, int in_w, float *w, int out_h, int out_w, int out_n,
+                               int out_c, float *C, float *Ww, const unsigned int n, int tiles_dim, int in_n,
+                               int tile_size, int in_c, int filt_k, int filt_c, int filt_h, int filt_w,
+                               int alpha, int m) {
+  (void)n;
+  if (filt_h != 3 || filt_w != 3 || m != 2 || tile_size != 4 || alpha != 4) return (int)cudaErrorInvalidValue;
+  if (filt_c != in_c || out_c != filt_k || out_n != in_n || out_h != in_h || out_w != in_w)
+    return (int)cudaErrorInvalidValue;
+  if (tiles_dim != (in_w + 1) / 2) return (int)cudaErrorInvalidValue;
+  return (int)forward(k, w, C, Ww, in_n, in_c, in_h, in_w, filt_k, OPENCNN_FP32, (cudaStream_t)0);
+}
+
+int convolutionForward(float *k, int in_h, int in_w, float *w, int out_h, int out_w, int out_n, int out_c,
+                       float *C, float *Ww, const unsigned int n, int tiles_dim, int in_n, int tile_size,
+                       int elems_dim, int in_c, int filt_k, int filt_c, int filt_h, int filt_w, int alpha,
+                       int m) {
+  (void)elems_dim;
+  return convolutionForward_32x64x8(k, in_h, in_w, w, out_h, out_w, out_n, out_c, C, Ww, n, tiles_dim, in_n,
+                                    tile_size, in_c, filt_k, filt_c, filt_h, filt_w, alpha, m);
+}
+
+int opencnn_convolutionForward_stream(const float *input, const float *filter, float *output, float *workspace,
+                                      int in_n, int in_c, int in_h, int in_w, int filt_k, int precision,
+                                      opencnn_stream_t stream) {
+  return (int)forward(input, filter, output, workspace, in_n, in_c, in_h, in_w, filt_k, precision,
+                      (cudaStream_t)stream);
+}
+
+int opencnn_filter_transform(const float *filter, float *workspace, int in_c, int filt_k, opencnn_stream_t stream) {
+  if (!filter || !workspace || !aligned16(filter) || !aligned16(workspace)) return (int)cudaErrorInvalidValue;
+  if (in_c <= 0 || filt_k <= 0 || filt_k % 4) return (int)cudaErrorInvalidValue;
+  return (int)launch_fx(filter, workspace, in_c, filt_k, (cudaStream_t)stream);
+}
+
+int opencnn_winograd_forward(const float *input, const float *workspace, float *output, int in_n, int in_c,
+                             int in_h, int in_w, int filt_k, int precision, opencnn_stream_t stream) {
+  if (!input || !workspace || !output) return (int)cudaErrorInvalidValue;
+  if (!aligned16(input) || !aligned16(workspace) || !aligned16(output)) return (int)cudaErrorInvalidValue;
+  cudaError_t e = check_shape(in_n, in_c, in_h, in_w, filt_k);
+  if (e != cudaSuccess) return (int)e;
+  if (precision != OPENCNN_FP32) return (int)cudaErrorNotSupported;
+  return (int)launch_wino_fp32(input, workspace, output, in_n, in_c, in_h, in_w, filt_k, (cudaStream_t)stream);
+}
+
+size_t opencnn_workspace_bytes(int in_c, int filt_k) {
+  if (in_c <= 0 || filt_k <= 0) return 0;
+  return (size_t)in_c * 16 * (size_t)filt_k * sizeof(float);
+}
+
+const char *opencnn_variant_name(void) { return OCB_VARIANT_NAME; }
+
+int opencnn_last_device_status(void) {
+  int v = -1;
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+  if (cudaMemcpyFromSymbol(&v, g_status, sizeof(int)) != cudaSuccess) return -1;
+  int zero = 0;
+  cudaMemcpyToSymbol(g_status, &zero, sizeof(int));
+  return v;
+}
+
+int opencnn_host_plan_create(void **plan, int in_n, int in_c, int in_h, int in_w, int filt_k, int precision) {
+  if (!plan) return (int)cudaErrorInvalidValue;
+  *plan = nullptr;
+  cudaError_t e = check_shape(in_n, in_c, in_h, in_w, filt_k);
+  if (e != cudaSuccess) return (int)e;
+  if (precision != OPENCNN_FP32) return (int)cudaErrorNotSupported;
+  HostPlan *hp = new (std::nothrow) HostPlan;
+  if (!hp) return (int)cudaErrorMemoryAllocation;
+  hp->N = in_n; hp->C = in_c; hp->H = in_h; hp->W = in_w; hp->K = filt_k; hp->precision = precision;
+  const size_t in_b = (size_t)in_n * in_c * in_h * in_w * 4, f_b = (size_t)in_c * 9 * filt_k * 4;
+  const size_t out_b = (size_t)in_n * filt_k * in_h * in_w * 4;
+  e = cudaMalloc(&hp->d_in, in_b);
+  if (e == cudaSuccess) e = cudaMalloc(&hp->d_filt, f_b);
+  if (e == cudaSuccess) e = cudaMalloc(&hp->d_out, out_b);
+  if (e == cudaSuccess) e = cudaMalloc(&hp->d_ws, opencnn_workspace_bytes(in_c, filt_k));
+  if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&hp->stream, cudaStreamNonBlocking);
+  if (e != cudaSuccess) {
+    opencnn_host_plan_destroy(hp);
+    return (int)e;
+  }
+  *plan = hp;
+  return 0;
+}
+
+int opencnn_host_plan_run(void *plan, const float *input_host, const float *filter_host, float *output_host) {
+  HostPlan *hp = static_cast<HostPlan *>(plan);
+  if (!hp || !input_host || !filter_host || !output_host) return (int)cudaErrorInvalidValue;
+  const size_t in_b = (size_t)hp->N * hp->C * hp->H * hp->W * 4, f_b = (size_t)hp->C * 9 * hp->K * 4;
+  const size_t out_b = (size_t)hp->N * hp->K * hp->H * hp->W * 4;
+  cudaError_t e = cudaMemcpyAsync(hp->d_filt, filter_host, f_b, cudaMemcpyHostToDevice, hp->stream);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(hp->d_in, input_host, in_b, cudaMemcpyHostToDevice, hp->stream);
+  if (e == cudaSuccess)
+    e = forward(hp->d_in, hp->d_filt, hp->d_out, hp->d_ws, hp->N, hp->C, hp->H, hp->W, hp->K, hp->precision, hp->stream);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(output_host, hp->d_out, out_b, cudaMemcpyDeviceToHost, hp->stream);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(hp->stream);
+  return (int)e;
+}
+
+int opencnn_host_plan_destroy(void *plan) {
+  HostPlan *hp = static_cast<HostPlan *>(plan);
+  if (!hp) return 0;
+  if (hp->d_in) cudaFree(hp->d_in);
+  if (hp->d_filt) cudaFree(hp->d_filt);
+  if (hp->d_out) cudaFree(hp->d_out);
+  if (hp->d_ws) cudaFree(hp->d_ws);
+  if (hp->stream) cudaStreamDestroy(hp->stream);
+  delete hp;
+  return 0;
+}
+
+}  // extern "C"
