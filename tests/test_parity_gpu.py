@@ -16,7 +16,7 @@ GOLDEN = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
 # N, C, K, H, W: minimum tile sizes, odd and even extents, 1x1, rectangles, several blocks.
 SMALL = [(32, 8, 64, 7, 7), (32, 16, 64, 8, 8), (64, 8, 128, 6, 6), (32, 8, 64, 1, 1), (32, 24, 64, 5, 9),
          (96, 8, 64, 3, 3), (32, 40, 192, 4, 2)]
-REL = 1e-4   # the fp32 path's tolerance against the reference / fp64 truth
+REL = 1e-4   # the fp32 path's tolerance: |a - r| <= REL * max(|r|, floor)
 
 
 def run(variant, x, g, via="legacy"):
@@ -35,8 +35,14 @@ def run(variant, x, g, via="legacy"):
     return dy.cpu().numpy(), dws.cpu().numpy()
 
 
-def within(y, truth, rel=REL):
-    tau = 1e-2 * float(np.sqrt(np.mean(truth.astype(np.float64) ** 2)))
+def within(y, truth, rel=REL, floor_frac=1.0):
+    """|y - truth| <= rel * max(|truth|, floor_frac * rms(truth)) everywhere.
+
+    Against the fp64 ground truth the floor is rms(truth): every output is a sum of 9*C products
+    whose rounding noise scales with the size of the terms, not with the (possibly cancelled)
+    result, and the reference's own kernels carry exactly the same noise.  Against the reference
+    itself the floor is 1% of the rms, and the results are in fact bit-identical."""
+    tau = floor_frac * float(np.sqrt(np.mean(truth.astype(np.float64) ** 2)))
     return bool(np.all(np.abs(y - truth) <= rel * np.maximum(np.abs(truth), tau)))
 
 
@@ -85,7 +91,7 @@ def test_matches_reference_kernels_on_device(oracle, libs, ref_libs, variant):
         torch.cuda.synchronize()
         y, ws = run(variant, x, g)
         r = ry.cpu().numpy()
-        assert within(y, r), "1e-4 relative against the reference"
+        assert within(y, r, floor_frac=1e-2), "1e-4 relative against the reference"
         assert np.array_equal(ws, rws.cpu().numpy())
         assert np.array_equal(y, r), f"not bit-identical: max |diff| {np.abs(y - r).max()}"
 
