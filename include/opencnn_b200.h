@@ -83,6 +83,12 @@ int opencnn_last_device_status(void);
  * asynchronous but is not required. */
 int opencnn_host_plan_create(void **plan, int in_n, int in_c, int in_h, int in_w, int filt_k, int precision);
 int opencnn_host_plan_run(void *plan, const float *input_host, const float *filter_host, float *output_host);
+/* The same work enqueued on the plan's own stream without waiting, and the matching wait: plans
+ * of different layers then overlap their uploads, kernels and downloads (pinned host memory
+ * required for overlap).  The host buffers must stay valid until opencnn_host_plan_wait. */
+int opencnn_host_plan_run_async(void *plan, const float *input_host, const float *filter_host,
+                                float *output_host);
+int opencnn_host_plan_wait(void *plan);
 int opencnn_host_plan_destroy(void *plan);
 
 #ifdef __cplusplus

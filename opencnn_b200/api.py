@@ -99,6 +99,12 @@ class HostPlan:
     def run(self, input_host_ptr: int, filter_host_ptr: int, output_host_ptr: int) -> int:
         return self._lib.opencnn_host_plan_run(self._h, input_host_ptr, filter_host_ptr, output_host_ptr)
 
+    def run_async(self, input_host_ptr: int, filter_host_ptr: int, output_host_ptr: int) -> int:
+        return self._lib.opencnn_host_plan_run_async(self._h, input_host_ptr, filter_host_ptr, output_host_ptr)
+
+    def wait(self) -> int:
+        return self._lib.opencnn_host_plan_wait(self._h)
+
     def close(self):
         if self._h:
             self._lib.opencnn_host_plan_destroy(self._h)

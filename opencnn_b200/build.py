@@ -66,9 +66,27 @@ def build_variant(variant: str, force: bool = False, verbose: bool = False) -> s
     return target
 
 
+def peaks_lib_path() -> str:
+    return os.path.join(LIBDIR, "libopencnn_b200_peaks.so")
+
+
+def build_peaks(force: bool = False) -> str:
+    """The FP32-pipe peak probe used by bench.py (csrc/peaks.cu); not part of the operator."""
+    os.makedirs(LIBDIR, exist_ok=True)
+    target, src = peaks_lib_path(), os.path.join(CSRC, "peaks.cu")
+    if force or not os.path.exists(target) or os.path.getmtime(src) > os.path.getmtime(target):
+        cmd = [nvcc(), *ARCH, "-O3", "-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC", "-shared", "-o", target, src]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"nvcc failed for peaks.cu:\n{res.stdout}\n{res.stderr}")
+    return target
+
+
 def build_all(force: bool = False, verbose: bool = False) -> list[str]:
-    with ThreadPoolExecutor(max_workers=4) as ex:
-        return list(ex.map(lambda v: build_variant(v, force, verbose), VARIANTS))
+    with ThreadPoolExecutor(max_workers=5) as ex:
+        peaks = ex.submit(build_peaks, force)
+        libs = list(ex.map(lambda v: build_variant(v, force, verbose), VARIANTS))
+        return libs + [peaks.result()]
 
 
 if __name__ == "__main__":

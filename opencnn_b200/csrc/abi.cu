@@ -250,7 +250,8 @@ int opencnn_host_plan_create(void **plan, int in_n, int in_c, int in_h, int in_w
   return 0;
 }
 
-int opencnn_host_plan_run(void *plan, const float *input_host, const float *filter_host, float *output_host) {
+int opencnn_host_plan_run_async(void *plan, const float *input_host, const float *filter_host,
+                                float *output_host) {
   HostPlan *hp = static_cast<HostPlan *>(plan);
   if (!hp || !input_host || !filter_host || !output_host) return (int)cudaErrorInvalidValue;
   const size_t in_b = (size_t)hp->N * hp->C * hp->H * hp->W * 4, f_b = (size_t)hp->C * 9 * hp->K * 4;
@@ -260,8 +261,18 @@ int opencnn_host_plan_run(void *plan, const float *input_host, const float *filt
   if (e == cudaSuccess)
     e = forward(hp->d_in, hp->d_filt, hp->d_out, hp->d_ws, hp->N, hp->C, hp->H, hp->W, hp->K, hp->precision, hp->stream);
   if (e == cudaSuccess) e = cudaMemcpyAsync(output_host, hp->d_out, out_b, cudaMemcpyDeviceToHost, hp->stream);
-  if (e == cudaSuccess) e = cudaStreamSynchronize(hp->stream);
   return (int)e;
+}
+
+int opencnn_host_plan_wait(void *plan) {
+  HostPlan *hp = static_cast<HostPlan *>(plan);
+  if (!hp) return (int)cudaErrorInvalidValue;
+  return (int)cudaStreamSynchronize(hp->stream);
+}
+
+int opencnn_host_plan_run(void *plan, const float *input_host, const float *filter_host, float *output_host) {
+  int e = opencnn_host_plan_run_async(plan, input_host, filter_host, output_host);
+  return e != 0 ? e : opencnn_host_plan_wait(plan);
 }
 
 int opencnn_host_plan_destroy(void *plan) {
