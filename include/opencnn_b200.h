@@ -76,6 +76,32 @@ const char *opencnn_variant_name(void);
  * reference has no counterpart: its kernels contain no waits. */
 int opencnn_last_device_status(void);
 
+/* The whole operator for callers that must not allocate.  (No counterpart in the reference: there
+ * the caller always cudaMallocs the workspace, src/openCNN_winograd.cu:309-311.)
+ *
+ * Some users of this library may not create device memory at the point where they convolve: a
+ * serving loop whose device memory is handed out once by the application's own pool, a plugin
+ * that is given its input and output tensors and nothing else, a process running under a fixed
+ * memory budget where a late cudaMalloc can fail or stall the device.  For them the
+ * transformed-filter workspace - the operator's only scratch memory - lives inside the library,
+ * in a static device array of OPENCNN_NOALLOC_MAX_CK * 16 floats (4 MiB) that every GPU which
+ * loads the library holds until the process exits.  The caller passes only input, filter and
+ * output.  The call makes no CUDA allocation and frees nothing.
+ *
+ * Limits and rules:
+ *  - in_c * filt_k must not exceed OPENCNN_NOALLOC_MAX_CK (65536, e.g. C = K = 256); larger
+ *    problems are refused with cudaErrorInvalidValue and a message on stderr.  Use the entry
+ *    points above with your own workspace for those.
+ *  - The first call on each device looks up the array's device address (and does the library's
+ *    usual one-time kernel set-up), so make that first call outside any stream capture.
+ *  - All calls on a device share the one array.  Nothing in it has to start at zero - every call
+ *    first overwrites the part it then reads - but it does keep the previous call's contents, and
+ *    two calls whose kernels overlap on the GPU (different streams, no ordering) race on it.
+ *    Order them on one stream or with events. */
+#define OPENCNN_NOALLOC_MAX_CK 65536
+int opencnn_convolutionForward_noalloc(const float *input, const float *filter, float *output, int in_n,
+                                       int in_c, int in_h, int in_w, int filt_k, opencnn_stream_t stream);
+
 /* Host-buffer front end, the shape of the reference's main() around the operator
  * (src/openCNN_winograd.cu:300-316 allocation, :470-472 copy back): a plan owns device buffers
  * for one problem size; run copies input and filter host->device, runs the operator, copies the

@@ -57,6 +57,18 @@ def conv3x3(input_chwn, filter_crsk, output_khwn, workspace, N, C, H, W, K, *, p
                                                  _ptr(workspace), N, C, H, W, K, PRECISIONS[precision], stream)
 
 
+NOALLOC_MAX_CK = 65536
+
+
+def conv3x3_noalloc(input_chwn, filter_crsk, output_khwn, N, C, H, W, K, *, stream=0, variant="OPTSTS64") -> int:
+    """The operator without a caller-supplied workspace (opencnn_convolutionForward_noalloc): the
+    transformed filter goes to a 4 MiB array built into the library, so the call allocates nothing.
+    Needs C*K <= NOALLOC_MAX_CK; calls that may overlap on the GPU must be ordered by the caller."""
+    lib = _lib.load(variant)
+    return lib.opencnn_convolutionForward_noalloc(_ptr(input_chwn), _ptr(filter_crsk), _ptr(output_khwn), N, C, H,
+                                                  W, K, stream)
+
+
 def call_like_reference(x, g, y, ws, N, C, H, W, K, *, variant="OPTSTS64") -> int:
     """Fills in the reference main()'s derived arguments (src/openCNN_winograd.cu:280-298, :429-431)."""
     td = tiles_dim(W)

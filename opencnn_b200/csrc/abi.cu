@@ -156,6 +156,34 @@ cudaError_t forward(const float *input, const float *filter, float *output, floa
   return launch_wino_fp32(input, workspace, output, N, C, H, W, K, stream);
 }
 
+// Scratch for opencnn_convolutionForward_noalloc: the transformed filter, [C][16][K] floats, for
+// problems up to OPENCNN_NOALLOC_MAX_CK channel-filter pairs.  In host code this name is only a
+// handle for the runtime, not a device address; the address is looked up once per device below.
+static __device__ __align__(256) float g_noalloc_workspace[(size_t)OPENCNN_NOALLOC_MAX_CK * 16];
+
+struct NoAllocState {
+  std::once_flag once;
+  cudaError_t error = cudaSuccess;
+  float *workspace = nullptr;     // device address of g_noalloc_workspace on this device
+};
+NoAllocState g_noalloc[kMaxDevices];
+
+// Device address of the static workspace on the current device (looked up on first use).
+cudaError_t noalloc_workspace(float **out) {
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= kMaxDevices) return cudaErrorInvalidDevice;
+  NoAllocState &st = g_noalloc[dev];
+  std::call_once(st.once, [&] {
+    void *p = nullptr;
+    st.error = cudaGetSymbolAddress(&p, g_noalloc_workspace);
+    if (st.error == cudaSuccess) st.workspace = static_cast<float *>(p);
+  });
+  *out = st.workspace;
+  return st.error;
+}
+
 struct HostPlan {
   int N, C, H, W, K, precision;
   float *d_in = nullptr, *d_filt = nullptr, *d_out = nullptr, *d_ws = nullptr;
@@ -208,6 +236,27 @@ int opencnn_winograd_forward(const float *input, const float *workspace, float *
   if (e != cudaSuccess) return (int)e;
   if (precision != OPENCNN_FP32) return (int)cudaErrorNotSupported;
   return (int)launch_wino_fp32(input, workspace, output, in_n, in_c, in_h, in_w, filt_k, (cudaStream_t)stream);
+}
+
+int opencnn_convolutionForward_noalloc(const float *input, const float *filter, float *output, int in_n,
+                                       int in_c, int in_h, int in_w, int filt_k, opencnn_stream_t stream) {
+  if (!input || !filter || !output) return (int)cudaErrorInvalidValue;
+  if (!aligned16(input) || !aligned16(filter) || !aligned16(output)) return (int)cudaErrorInvalidValue;
+  cudaError_t e = check_shape(in_n, in_c, in_h, in_w, filt_k);
+  if (e != cudaSuccess) return (int)e;
+  if ((long long)in_c * filt_k > (long long)OPENCNN_NOALLOC_MAX_CK) {
+    std::fprintf(stderr,
+                 "opencnn_convolutionForward_noalloc: in_c*filt_k = %lld exceeds the built-in workspace "
+                 "(OPENCNN_NOALLOC_MAX_CK = %d); use opencnn_convolutionForward_stream with your own workspace\n",
+                 (long long)in_c * filt_k, OPENCNN_NOALLOC_MAX_CK);
+    return (int)cudaErrorInvalidValue;
+  }
+  float *ws = nullptr;
+  e = noalloc_workspace(&ws);
+  if (e != cudaSuccess) return (int)e;
+  e = launch_fx(filter, ws, in_c, filt_k, (cudaStream_t)stream);
+  if (e != cudaSuccess) return (int)e;
+  return (int)launch_wino_fp32(input, ws, output, in_n, in_c, in_h, in_w, filt_k, (cudaStream_t)stream);
 }
 
 size_t opencnn_workspace_bytes(int in_c, int filt_k) {
