@@ -157,7 +157,14 @@ def main():
     ap.add_argument("--precision", default="fp32", choices=["fp32", "tf32", "bf16"])
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--layers", default=None,
+                    help="override the workload, e.g. '64,64,64,56;128,256,256,14' (N,C,K,H=W per layer); "
+                         "for profiling small cases, not for reported numbers")
     args = ap.parse_args()
+    global LAYERS, WORKLOAD
+    if args.layers:
+        LAYERS = [tuple(int(v) for v in item.split(",")) for item in args.layers.split(";")]
+        WORKLOAD = "custom: " + args.layers
     if args.warmup < 3:
         args.warmup = 3
 
@@ -360,7 +367,7 @@ def main():
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32" if args.precision == "fp32" else args.precision, "data": "synthetic",
-            "config": {"workload": WORKLOAD, "images_per_gpu": 128, "global_batch": 128 * world,
+            "config": {"workload": WORKLOAD, "images_per_gpu": LAYERS[0][0], "global_batch": LAYERS[0][0] * world,
                        "variant": args.variant, "precision": args.precision, "parallelism": f"batch-sharded x{world}",
                        "l2": "each layer has its own buffers; one step touches 398 MB > 126 MB L2 before a buffer is reused",
                        "us_per_layer": ms_per_step * 1e3 / len(LAYERS)},
