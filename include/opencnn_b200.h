@@ -60,6 +60,11 @@ int opencnn_convolutionForward_stream(const float *input, const float *filter, f
  * weights can transform once and reuse the workspace. */
 int opencnn_filter_transform(const float *filter, float *workspace, int in_c, int filt_k,
                              opencnn_stream_t stream);
+/* The same for a given arithmetic: the TF32 / BF16 workspace holds the transformed filter rounded
+ * to the tensor-core operand type (and is what opencnn_winograd_forward expects for that
+ * precision). */
+int opencnn_filter_transform_p(const float *filter, float *workspace, int in_c, int filt_k, int precision,
+                               opencnn_stream_t stream);
 int opencnn_winograd_forward(const float *input, const float *workspace, float *output, int in_n, int in_c,
                              int in_h, int in_w, int filt_k, int precision, opencnn_stream_t stream);
 

@@ -21,6 +21,7 @@ SIGNATURES = {
                                    c_void_p, c_uint] + [c_int] * 11),
     "opencnn_convolutionForward_stream": (c_int, [c_void_p] * 4 + [c_int] * 6 + [c_void_p]),
     "opencnn_filter_transform": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "opencnn_filter_transform_p": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "opencnn_winograd_forward": (c_int, [c_void_p] * 3 + [c_int] * 6 + [c_void_p]),
     "opencnn_convolutionForward_noalloc": (c_int, [c_void_p] * 3 + [c_int] * 5 + [c_void_p]),
     "opencnn_workspace_bytes": (c_size_t, [c_int, c_int]),

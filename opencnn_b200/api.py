@@ -76,8 +76,9 @@ def call_like_reference(x, g, y, ws, N, C, H, W, K, *, variant="OPTSTS64") -> in
                               variant=variant)
 
 
-def filter_transform(filter_crsk, workspace, C, K, *, stream=0, variant="OPTSTS64") -> int:
-    return _lib.load(variant).opencnn_filter_transform(_ptr(filter_crsk), _ptr(workspace), C, K, stream)
+def filter_transform(filter_crsk, workspace, C, K, *, precision="fp32", stream=0, variant="OPTSTS64") -> int:
+    return _lib.load(variant).opencnn_filter_transform_p(_ptr(filter_crsk), _ptr(workspace), C, K,
+                                                         PRECISIONS[precision], stream)
 
 
 def winograd_forward(input_chwn, workspace, output_khwn, N, C, H, W, K, *, precision="fp32", stream=0,

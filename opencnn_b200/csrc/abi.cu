@@ -12,6 +12,7 @@
 #include "../../include/opencnn_b200.h"
 #include "fx.cuh"
 #include "wino_fp32.cuh"
+#include "wino_tc.cuh"
 
 #if defined(BASE)
 #define OCB_VARIANT ocb::kBase
@@ -72,6 +73,12 @@ cudaError_t device_state(DeviceState **out) {
     if (err == cudaSuccess)
       err = cudaFuncSetAttribute(ocb::wino_fp32_kernel<OCB_VARIANT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)ocb::SmemLayout<OCB_VARIANT>::kBytes);
+    if (err == cudaSuccess)
+      err = cudaFuncSetAttribute(ocb::wino_tc_kernel<ocb::kTcBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)ocb::TcCfg<ocb::kTcBf16>::kSmemBytes);
+    if (err == cudaSuccess)
+      err = cudaFuncSetAttribute(ocb::wino_tc_kernel<ocb::kTcTf32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)ocb::TcCfg<ocb::kTcTf32>::kSmemBytes);
     if (err == cudaSuccess) err = cudaGetSymbolAddress(reinterpret_cast<void **>(&st.status_ptr), g_status);
     st.init_error = err;
   });
@@ -144,13 +151,85 @@ cudaError_t launch_wino_fp32(const float *input, const float *workspace, float *
   return cudaGetLastError();
 }
 
+// Tensor-core path: filter transform rounded to the operand type, then the tcgen05 kernel.
+template <int DT>
+cudaError_t launch_fx_tc(const float *filter, float *workspace, int C, int K, cudaStream_t stream) {
+  const int k4 = K / 4;
+  const int total = C * k4;
+  ocb::fx_tc_kernel<DT><<<(total + 127) / 128, 128, 0, stream>>>(reinterpret_cast<const float4 *>(filter), workspace, C, k4);
+  return cudaGetLastError();
+}
+
+template <int DT>
+cudaError_t launch_wino_tc(const float *input, const float *workspace, float *output, int N, int C, int H, int W,
+                           int K, cudaStream_t stream) {
+  DeviceState *st = nullptr;
+  cudaError_t e = device_state(&st);
+  if (e != cudaSuccess) return e;
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return cudaErrorNotSupported;
+  constexpr int KC = ocb::TcCfg<DT>::kKC;
+  constexpr bool bf16 = DT == ocb::kTcBf16;
+  constexpr cuuint64_t esz = bf16 ? 2 : 4;
+  constexpr cuuint32_t row_elems = bf16 ? 64 : 32;            // filters in one 128-byte row
+
+  CUtensorMap tm_in, tm_u;
+  {
+    cuuint64_t dims[4] = {(cuuint64_t)N, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)C};
+    cuuint64_t strides[3] = {(cuuint64_t)N * 4, (cuuint64_t)W * N * 4, (cuuint64_t)H * W * N * 4};
+    cuuint32_t box[4] = {(cuuint32_t)ocb::kTcN, 4, 4, (cuuint32_t)KC};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    if (enc(&tm_in, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(input), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return cudaErrorInvalidValue;
+  }
+  {
+    // workspace [C][16][K] viewed as {filter within a 128-byte row, channel, 128-byte row, position}
+    cuuint64_t dims[4] = {row_elems, (cuuint64_t)C, (cuuint64_t)K / row_elems, 16};
+    cuuint64_t strides[3] = {(cuuint64_t)16 * K * esz, 128, (cuuint64_t)K * esz};
+    cuuint32_t box[4] = {row_elems, (cuuint32_t)KC, (cuuint32_t)(ocb::kTcM / row_elems), 16};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    if (enc(&tm_u, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4,
+            const_cast<float *>(workspace), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            bf16 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return cudaErrorInvalidValue;
+  }
+  ocb::WinoParams p;
+  p.y = output;
+  p.N = N; p.C = C; p.K = K; p.H = H; p.W = W;
+  p.tiles_h = (H + 1) / 2;
+  p.tiles_w = (W + 1) / 2;
+  p.n_blocks = N / ocb::kTcN;
+  p.k_blocks = (K + ocb::kTcM - 1) / ocb::kTcM;
+  const long long tiles = (long long)p.tiles_h * p.tiles_w * p.n_blocks * p.k_blocks;
+  if (tiles > 0x7fffffffll / 8) return cudaErrorInvalidValue;
+  p.total_tiles = (int)tiles;
+  p.chunks_per_tile = (C + KC - 1) / KC;
+  p.status = st->status_ptr;
+  const int grid = p.total_tiles < st->sm_count ? p.total_tiles : st->sm_count;
+  ocb::wino_tc_kernel<DT><<<grid, ocb::kTcThreads, ocb::TcCfg<DT>::kSmemBytes, stream>>>(tm_in, tm_u, p);
+  return cudaGetLastError();
+}
+
 cudaError_t forward(const float *input, const float *filter, float *output, float *workspace, int N, int C, int H,
                     int W, int K, int precision, cudaStream_t stream) {
   if (!input || !filter || !output || !workspace) return cudaErrorInvalidValue;
   if (!aligned16(input) || !aligned16(filter) || !aligned16(output) || !aligned16(workspace)) return cudaErrorInvalidValue;
   cudaError_t e = check_shape(N, C, H, W, K);
   if (e != cudaSuccess) return e;
-  if (precision != OPENCNN_FP32) return cudaErrorNotSupported;
+  if (precision == OPENCNN_BF16) {
+    e = launch_fx_tc<ocb::kTcBf16>(filter, workspace, C, K, stream);
+    if (e != cudaSuccess) return e;
+    return launch_wino_tc<ocb::kTcBf16>(input, workspace, output, N, C, H, W, K, stream);
+  }
+  if (precision == OPENCNN_TF32) {
+    e = launch_fx_tc<ocb::kTcTf32>(filter, workspace, C, K, stream);
+    if (e != cudaSuccess) return e;
+    return launch_wino_tc<ocb::kTcTf32>(input, workspace, output, N, C, H, W, K, stream);
+  }
+  if (precision != OPENCNN_FP32) return cudaErrorInvalidValue;
   e = launch_fx(filter, workspace, C, K, stream);
   if (e != cudaSuccess) return e;
   return launch_wino_fp32(input, workspace, output, N, C, H, W, K, stream);
@@ -223,8 +302,16 @@ int opencnn_convolutionForward_stream(const float *input, const float *filter, f
 }
 
 int opencnn_filter_transform(const float *filter, float *workspace, int in_c, int filt_k, opencnn_stream_t stream) {
+  return opencnn_filter_transform_p(filter, workspace, in_c, filt_k, OPENCNN_FP32, stream);
+}
+
+int opencnn_filter_transform_p(const float *filter, float *workspace, int in_c, int filt_k, int precision,
+                               opencnn_stream_t stream) {
   if (!filter || !workspace || !aligned16(filter) || !aligned16(workspace)) return (int)cudaErrorInvalidValue;
   if (in_c <= 0 || filt_k <= 0 || filt_k % 4) return (int)cudaErrorInvalidValue;
+  if (precision == OPENCNN_BF16) return (int)launch_fx_tc<ocb::kTcBf16>(filter, workspace, in_c, filt_k, (cudaStream_t)stream);
+  if (precision == OPENCNN_TF32) return (int)launch_fx_tc<ocb::kTcTf32>(filter, workspace, in_c, filt_k, (cudaStream_t)stream);
+  if (precision != OPENCNN_FP32) return (int)cudaErrorInvalidValue;
   return (int)launch_fx(filter, workspace, in_c, filt_k, (cudaStream_t)stream);
 }
 
@@ -234,7 +321,11 @@ int opencnn_winograd_forward(const float *input, const float *workspace, float *
   if (!aligned16(input) || !aligned16(workspace) || !aligned16(output)) return (int)cudaErrorInvalidValue;
   cudaError_t e = check_shape(in_n, in_c, in_h, in_w, filt_k);
   if (e != cudaSuccess) return (int)e;
-  if (precision != OPENCNN_FP32) return (int)cudaErrorNotSupported;
+  if (precision == OPENCNN_BF16)
+    return (int)launch_wino_tc<ocb::kTcBf16>(input, workspace, output, in_n, in_c, in_h, in_w, filt_k, (cudaStream_t)stream);
+  if (precision == OPENCNN_TF32)
+    return (int)launch_wino_tc<ocb::kTcTf32>(input, workspace, output, in_n, in_c, in_h, in_w, filt_k, (cudaStream_t)stream);
+  if (precision != OPENCNN_FP32) return (int)cudaErrorInvalidValue;
   return (int)launch_wino_fp32(input, workspace, output, in_n, in_c, in_h, in_w, filt_k, (cudaStream_t)stream);
 }
 
@@ -280,7 +371,7 @@ int opencnn_host_plan_create(void **plan, int in_n, int in_c, int in_h, int in_w
   *plan = nullptr;
   cudaError_t e = check_shape(in_n, in_c, in_h, in_w, filt_k);
   if (e != cudaSuccess) return (int)e;
-  if (precision != OPENCNN_FP32) return (int)cudaErrorNotSupported;
+  if (precision != OPENCNN_FP32 && precision != OPENCNN_TF32 && precision != OPENCNN_BF16) return (int)cudaErrorInvalidValue;
   HostPlan *hp = new (std::nothrow) HostPlan;
   if (!hp) return (int)cudaErrorMemoryAllocation;
   hp->N = in_n; hp->C = in_c; hp->H = in_h; hp->W = in_w; hp->K = filt_k; hp->precision = precision;

@@ -1,0 +1,375 @@
+// Fused Winograd F(2x2,3x3) forward kernel with the 16 batched GEMMs on the 5th-generation
+// tensor cores (tcgen05.mma, accumulators in TMEM), operands in BF16 or TF32, fp32 accumulate.
+//
+// Same operator as wino_fp32.cuh - it replaces the reference's Winograd_kernel
+// (src/convolutionForward_32x64x8.cu:169-262) - but only the contraction of its main loop
+// (outer_product, src/outer_product.cuh) moves to the tensor cores; the input and output
+// transforms stay in fp32 on the CUDA cores.  The reference has no tensor-core path.
+//
+// One CTA tile = 128 filters x 32 images x one 2x2-output tile, all 16 Winograd positions: the
+// 16 accumulators D[xi] (128 x 32 fp32 each) fill the SM's tensor memory exactly (512 columns).
+// Filters are the M dimension of the MMA, images the N dimension, channels the K dimension:
+//   D[xi][k][n] += sum_c U[xi][k][c] * V[xi][n][c]
+// Both operands are "MN-major" in shared memory (M resp. N contiguous), which is how they exist
+// anyway: U rows of consecutive filters come straight from the transformed-filter workspace by
+// TMA (128-byte swizzle), V rows of consecutive images are written by the transform threads.
+// Per K-step (16 channels in BF16, 8 in TF32) one elected thread issues 16 MMAs.
+//
+// Warp roles (320 threads):
+//   warp 0      TMA: raw input patches (4-D box, hardware zero-fill = halo) and U slices
+//   warps 1-4   input transform B^T d B in fp32, rounding, V written in the UMMA layout
+//   warp 5      MMA issue, tcgen05.commit to free stages and to publish a finished tile;
+//               also owns the TMEM allocation
+//   warps 6-9   epilogue: tcgen05.ld the 16 positions of (filter = TMEM lane, 4 images),
+//               A^T M A in registers - no shared-memory transpose - 16-byte stores
+// All hand-offs are mbarriers with bounded waits.
+#pragma once
+#include "fx.cuh"
+#include "ptx.cuh"
+#include "wino_fp32.cuh"   // WinoParams, TileCoord, output_transform, add2/sub2
+
+namespace ocb {
+
+enum TcType : int { kTcBf16 = 0, kTcTf32 = 1 };
+
+constexpr int kTcThreads = 320;
+constexpr int kTcM = 128;                   // filters per CTA tile
+constexpr int kTcN = 32;                    // images per CTA tile
+constexpr int kTcStages = 2;
+constexpr uint32_t kTcUBytes = 16 * 4096;   // 16 positions x (128 filters x one K-step)
+constexpr uint32_t kTcVBytes = 16 * 1024;   // 16 positions x (32 images x one K-step)
+
+template <int DT> struct TcCfg {
+  static constexpr int kKC = DT == kTcBf16 ? 16 : 8;                 // channels per K-step / stage
+  static constexpr uint32_t kRawBytes = kKC * 16 * kTcN * 4;         // [c][h][w][n] fp32
+  static constexpr size_t kSmemBytes = (size_t)kTcStages * (kRawBytes + kTcUBytes + kTcVBytes) + 1024;
+};
+
+// ---- tcgen05 wrappers ------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc_512(uint32_t smem_dst) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_dst) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_512(uint32_t taddr) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+template <int DT>
+__device__ __forceinline__ void tc_mma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  if (DT == kTcBf16) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+  }
+}
+__device__ __forceinline__ void tmem_ld_x4(uint32_t taddr, float (&v)[4]) {
+  uint32_t r0, r1, r2, r3;
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(taddr) : "memory");
+  v[0] = __uint_as_float(r0); v[1] = __uint_as_float(r1); v[2] = __uint_as_float(r2); v[3] = __uint_as_float(r3);
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor (sm_100 format): start address, leading / stride byte offsets
+// (all in 16-byte units), version 1, swizzle mode (2 = 128 B, 4 = 64 B, 6 = 32 B, 0 = none,
+// 1 = 128 B with 32-byte atoms).
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
+  return (uint64_t)((addr >> 4) & 0x3FFFu) | ((uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16) |
+         ((uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32) | (1ull << 46) | ((uint64_t)layout << 61);
+}
+// Instruction descriptor: fp32 accumulate, A and B of the same format, both MN-major, M x N.
+template <int DT> __device__ __forceinline__ uint32_t instr_desc() {
+  const uint32_t fmt = DT == kTcBf16 ? 1u : 2u;
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 15) | (1u << 16) | ((uint32_t)(kTcN >> 3) << 17) |
+         ((uint32_t)(kTcM >> 4) << 24);
+}
+
+__device__ __forceinline__ float round_tf32_rne(float v) {
+  uint32_t u = __float_as_uint(v);
+  u += 0xFFFu + ((u >> 13) & 1u);
+  return __uint_as_float(u & 0xFFFFE000u);
+}
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+// ---- filter transform for the tensor-core path ------------------------------------------------
+// Same arithmetic as fx_kernel, then one rounding to the operand type.  Output [C][16][K]:
+// BF16 packed, or fp32 words holding TF32 values (low 13 mantissa bits zero).
+template <int DT>
+__global__ void __launch_bounds__(128) fx_tc_kernel(const float4 *__restrict__ g, void *__restrict__ U, int C, int k4) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= C * k4) return;
+  const int c = idx / k4, kq = idx - c * k4;
+  const float4 *src = g + (size_t)c * 9 * k4 + kq;
+  float4 in[9];
+#pragma unroll
+  for (int i = 0; i < 9; ++i) in[i] = __ldg(src + (size_t)i * k4);
+  float wx[9], wy[9], wz[9], ww[9];
+#pragma unroll
+  for (int i = 0; i < 9; ++i) { wx[i] = in[i].x; wy[i] = in[i].y; wz[i] = in[i].z; ww[i] = in[i].w; }
+  float ux[16], uy[16], uz[16], uw[16];
+  fx_one(wx, ux); fx_one(wy, uy); fx_one(wz, uz); fx_one(ww, uw);
+  if (DT == kTcBf16) {
+    uint2 *dst = reinterpret_cast<uint2 *>(U) + (size_t)c * 16 * k4 + kq;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) dst[(size_t)i * k4] = make_uint2(pack_bf16x2(ux[i], uy[i]), pack_bf16x2(uz[i], uw[i]));
+  } else {
+    float4 *dst = reinterpret_cast<float4 *>(U) + (size_t)c * 16 * k4 + kq;
+#pragma unroll
+    for (int i = 0; i < 16; ++i)
+      dst[(size_t)i * k4] = make_float4(round_tf32_rne(ux[i]), round_tf32_rne(uy[i]), round_tf32_rne(uz[i]), round_tf32_rne(uw[i]));
+  }
+}
+
+// ---- input transform into the V operand --------------------------------------------------------
+// BF16: item = (channel c of the stage, image pair np); V tile of a position is [16 c][32 n] bf16,
+// rows of 64 bytes, 64-byte swizzle (16-byte chunk index ^= (c >> 1) & 3).
+__device__ __forceinline__ void transform_to_v_bf16(const float *raw, uint8_t *vst, int c, int np) {
+  const uint64_t *R = reinterpret_cast<const uint64_t *>(raw + (c * 16) * kTcN + 2 * np);
+  constexpr int P = kTcN / 2;
+  uint64_t d[16], b[16];
+#pragma unroll
+  for (int q = 0; q < 16; ++q) d[q] = R[q * P];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    b[j] = sub2(d[j], d[8 + j]);
+    b[4 + j] = add2(d[4 + j], d[8 + j]);
+    b[8 + j] = sub2(d[8 + j], d[4 + j]);
+    b[12 + j] = sub2(d[4 + j], d[12 + j]);
+  }
+  uint8_t *dst = vst + c * 64 + ((((np >> 2) ^ (c >> 1)) & 3) << 4) + ((np & 3) << 2);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint64_t o[4];
+    o[0] = sub2(b[4 * i + 0], b[4 * i + 2]);
+    o[1] = add2(b[4 * i + 1], b[4 * i + 2]);
+    o[2] = sub2(b[4 * i + 2], b[4 * i + 1]);
+    o[3] = sub2(b[4 * i + 1], b[4 * i + 3]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float lo, hi;
+      unpack2(o[j], lo, hi);
+      *reinterpret_cast<uint32_t *>(dst + (4 * i + j) * 1024) = pack_bf16x2(lo, hi);
+    }
+  }
+}
+// TF32: item = (channel c of the stage, image n); V tile of a position is [8 c][32 n] fp32, rows
+// of 128 bytes, in the "128-byte swizzle with 32-byte atoms" pattern that MN-major 32-bit operands
+// need (32-byte chunk index ^= c & 3; the pattern repeats every 4 rows).
+__device__ __forceinline__ void transform_to_v_tf32(const float *raw, uint8_t *vst, int c, int n) {
+  const float *R = raw + (c * 16) * kTcN + n;
+  float d[16], b[16];
+#pragma unroll
+  for (int q = 0; q < 16; ++q) d[q] = R[q * kTcN];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    b[j] = __fsub_rn(d[j], d[8 + j]);
+    b[4 + j] = __fadd_rn(d[4 + j], d[8 + j]);
+    b[8 + j] = __fsub_rn(d[8 + j], d[4 + j]);
+    b[12 + j] = __fsub_rn(d[4 + j], d[12 + j]);
+  }
+  uint8_t *dst = vst + c * 128 + ((((n >> 3) ^ c) & 3) << 5) + ((n & 7) << 2);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float o[4];
+    o[0] = __fsub_rn(b[4 * i + 0], b[4 * i + 2]);
+    o[1] = __fadd_rn(b[4 * i + 1], b[4 * i + 2]);
+    o[2] = __fsub_rn(b[4 * i + 2], b[4 * i + 1]);
+    o[3] = __fsub_rn(b[4 * i + 1], b[4 * i + 3]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) *reinterpret_cast<float *>(dst + (4 * i + j) * 1024) = round_tf32_rne(o[j]);
+  }
+}
+
+// p.k_blocks counts 128-filter blocks here.
+template <int DT>
+__global__ void __launch_bounds__(kTcThreads, 1)
+wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ CUtensorMap tm_u, const WinoParams p) {
+  using Cfg = TcCfg<DT>;
+  constexpr int KC = Cfg::kKC;
+  extern __shared__ __align__(1024) uint8_t tsmem[];
+  uint8_t *raw_s = tsmem;                                              // [stage][KC][16][32] fp32
+  uint8_t *u_s = raw_s + kTcStages * Cfg::kRawBytes;                   // [stage][16 xi][...]  4 KB per position
+  uint8_t *v_s = u_s + kTcStages * kTcUBytes;                          // [stage][16 xi][...]  1 KB per position
+  uint64_t *bars = reinterpret_cast<uint64_t *>(v_s + kTcStages * kTcVBytes);
+  uint64_t *raw_full = bars, *raw_empty = bars + 2, *u_full = bars + 4, *v_ready = bars + 6, *uv_empty = bars + 8;
+  uint64_t *acc_full = bars + 10, *acc_empty = bars + 11;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 12);
+  volatile int *dead = reinterpret_cast<volatile int *>(bars + 13);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int my_tiles = (p.total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+  const int cpt = p.chunks_per_tile;
+  const int total_chunks = my_tiles * cpt;
+
+  if (tid == 0) {
+    *dead = 0;
+    for (int s = 0; s < kTcStages; ++s) {
+      mbar_init(smem_u32(raw_full + s), 1);
+      mbar_init(smem_u32(raw_empty + s), 4);
+      mbar_init(smem_u32(u_full + s), 1);
+      mbar_init(smem_u32(v_ready + s), 4);
+      mbar_init(smem_u32(uv_empty + s), 1);
+    }
+    mbar_init(smem_u32(acc_full), 1);
+    mbar_init(smem_u32(acc_empty), 4);
+    mbar_fence_init();
+  }
+  if (warp == 5) tmem_alloc_512(smem_u32(tmem_slot));
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ===================================== TMA producer ========================================
+    if (lane == 0) {
+      tma_prefetch_descriptor(&tm_in);
+      tma_prefetch_descriptor(&tm_u);
+      int seq = 0, ci = 0;
+      TileCoord tc = decode_tile(p, (int)blockIdx.x);
+      for (int g = 0; g < total_chunks; ++g) {
+        const int s = g % kTcStages;
+        const uint32_t use = g / kTcStages;
+        if (use > 0) mbar_wait(smem_u32(raw_empty + s), (use - 1) & 1, dead, p.status);
+        mbar_arrive_expect_tx(smem_u32(raw_full + s), Cfg::kRawBytes);
+        tma_load_4d(smem_u32(raw_s + s * Cfg::kRawBytes), &tm_in, smem_u32(raw_full + s), tc.nb * kTcN, 2 * tc.tx - 1,
+                    2 * tc.ty - 1, ci * KC);
+        if (use > 0) mbar_wait(smem_u32(uv_empty + s), (use - 1) & 1, dead, p.status);
+        mbar_arrive_expect_tx(smem_u32(u_full + s), kTcUBytes);
+        // U viewed as {filters within a 128-byte row, channel, 128-byte row of the filter axis, position}
+        tma_load_4d(smem_u32(u_s + s * kTcUBytes), &tm_u, smem_u32(u_full + s), 0, ci * KC,
+                    tc.kb * (DT == kTcBf16 ? 2 : 4), 0);
+        if (++ci == cpt) {
+          ci = 0;
+          ++seq;
+          if (seq < my_tiles) tc = decode_tile(p, (int)blockIdx.x + seq * (int)gridDim.x);
+        }
+      }
+    }
+  } else if (warp <= 4) {
+    // ===================================== input transform =====================================
+    const int t = tid - 32;                                            // 0..127
+    for (int g = 0; g < total_chunks; ++g) {
+      const int s = g % kTcStages;
+      const uint32_t use = g / kTcStages;
+      mbar_wait(smem_u32(raw_full + s), use & 1, dead, p.status);
+      if (use > 0) mbar_wait(smem_u32(uv_empty + s), (use - 1) & 1, dead, p.status);   // V stage free again
+      const float *raw = reinterpret_cast<const float *>(raw_s + s * Cfg::kRawBytes);
+      uint8_t *vst = v_s + s * kTcVBytes;
+      if (DT == kTcBf16) {
+        transform_to_v_bf16(raw, vst, t >> 4, t & 15);
+        transform_to_v_bf16(raw, vst, (t >> 4) + 8, t & 15);
+      } else {
+        transform_to_v_tf32(raw, vst, t >> 5, t & 31);
+        transform_to_v_tf32(raw, vst, (t >> 5) + 4, t & 31);
+      }
+      fence_proxy_async_smem();          // V is read by the tensor core through the async proxy
+      __syncwarp();
+      if (lane == 0) {
+        mbar_arrive(smem_u32(raw_empty + s));
+        mbar_arrive(smem_u32(v_ready + s));
+      }
+    }
+  } else if (warp == 5) {
+    // ===================================== MMA issuer ==========================================
+    if (lane == 0) {
+      const uint32_t idesc = instr_desc<DT>();
+      int ci = 0, seq = 0;
+      for (int g = 0; g < total_chunks; ++g) {
+        const int s = g % kTcStages;
+        const uint32_t use = g / kTcStages;
+        mbar_wait(smem_u32(u_full + s), use & 1, dead, p.status);
+        mbar_wait(smem_u32(v_ready + s), use & 1, dead, p.status);
+        if (ci == 0 && seq > 0) mbar_wait(smem_u32(acc_empty), (seq - 1) & 1, dead, p.status);   // TMEM drained
+        tc_fence_after();
+        const uint32_t ua = smem_u32(u_s + s * kTcUBytes), va = smem_u32(v_s + s * kTcVBytes);
+#pragma unroll 1
+        for (int xi = 0; xi < 16; ++xi) {
+          // A: 128 filters x KC channels, filter-contiguous rows of 128 B (64 bf16 / 32 tf32 filters), 8-channel
+          //    groups 1 KB apart, 128-byte-row blocks of the filter axis KC*128 B apart.
+          // B: 32 images x KC channels, image-contiguous rows (64 B bf16 / 128 B tf32), 8-channel groups 512 B apart.
+          // TF32 (32-bit, MN-major) uses the 128B-swizzle-with-32B-atom mode: 4-channel groups 512 B apart.
+          const uint64_t adesc = DT == kTcBf16 ? smem_desc(ua + xi * 4096, KC * 128, 1024, 2)
+                                               : smem_desc(ua + xi * 4096, KC * 128, 512, 1);
+          const uint64_t bdesc = DT == kTcBf16 ? smem_desc(va + xi * 1024, 512, 512, 4)
+                                               : smem_desc(va + xi * 1024, 1024, 512, 1);
+          tc_mma<DT>(tmem_base + xi * kTcN, adesc, bdesc, idesc, ci > 0 ? 1u : 0u);
+        }
+        tc_commit(smem_u32(uv_empty + s));                 // stage reusable when these MMAs are done
+        if (++ci == cpt) {
+          tc_commit(smem_u32(acc_full));                   // tile finished
+          ci = 0;
+          ++seq;
+        }
+      }
+    }
+  } else {
+    // ===================================== epilogue ============================================
+    const int quarter = warp & 3;                                        // TMEM lanes this warp may read
+    const int m = quarter * 32 + lane;                                   // filter within the tile
+    const size_t plane = (size_t)p.H * p.W * p.N;
+    const size_t dW = (size_t)p.N, dH = (size_t)p.W * p.N;
+    for (int seq = 0; seq < my_tiles; ++seq) {
+      const TileCoord tc = decode_tile(p, (int)blockIdx.x + seq * (int)gridDim.x);
+      mbar_wait(smem_u32(acc_full), seq & 1, dead, p.status);
+      tc_fence_after();
+      const int k = tc.kb * kTcM + m;
+      const bool valid = k < p.K;
+      const int oh0 = 2 * tc.ty, ow0 = 2 * tc.tx;
+      const bool row1 = (oh0 + 1) < p.H, col1 = (ow0 + 1) < p.W;
+      float *ybase = p.y + (size_t)k * plane + ((size_t)oh0 * p.W + ow0) * p.N + (size_t)tc.nb * kTcN;
+      const uint32_t tlane = tmem_base + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+      for (int j = 0; j < kTcN / 4; ++j) {
+        float mm[16][4];
+#pragma unroll
+        for (int xi = 0; xi < 16; ++xi) tmem_ld_x4(tlane + xi * kTcN + 4 * j, mm[xi]);
+        tmem_ld_wait();
+        float y00[4], y01[4], y10[4], y11[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float col[16], yy[4];
+#pragma unroll
+          for (int xi = 0; xi < 16; ++xi) col[xi] = mm[xi][e];
+          output_transform(col, yy);
+          y00[e] = yy[0]; y01[e] = yy[1]; y10[e] = yy[2]; y11[e] = yy[3];
+        }
+        if (valid) {
+          float *dst = ybase + 4 * j;
+          *reinterpret_cast<float4 *>(dst) = make_float4(y00[0], y00[1], y00[2], y00[3]);
+          if (col1) *reinterpret_cast<float4 *>(dst + dW) = make_float4(y01[0], y01[1], y01[2], y01[3]);
+          if (row1) {
+            *reinterpret_cast<float4 *>(dst + dH) = make_float4(y10[0], y10[1], y10[2], y10[3]);
+            if (col1) *reinterpret_cast<float4 *>(dst + dH + dW) = make_float4(y11[0], y11[1], y11[2], y11[3]);
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(acc_empty));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc_512(tmem_base);
+  }
+}
+
+}  // namespace ocb

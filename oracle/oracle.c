@@ -316,6 +316,87 @@ static inline float oc_round_bits(float v, int drop) {
 OC_API void oc_round_tf32(float *a, size_t count) { for (size_t i = 0; i < count; ++i) a[i] = oc_round_bits(a[i], 13); }
 OC_API void oc_round_bf16(float *a, size_t count) { for (size_t i = 0; i < count; ++i) a[i] = oc_round_bits(a[i], 16); }
 
+static inline float oc_round_bits(float v, int drop);
+
+/* Model of the tensor-core path: filter and input transforms in fp32 exactly as above, each
+ * transformed value rounded once to the operand type (mode 1 = TF32, 2 = BF16, 0 = none), the
+ * contraction over channels exact (double), the output transform in fp32.  The device
+ * accumulates in fp32 inside the tensor core, so agreement is to ~1e-5 relative, not bitwise.
+ * This path has no counterpart in the reference; the model states what the kernel is meant to
+ * compute so that layout or indexing mistakes cannot hide behind the quantisation error. */
+OC_API void oc_winograd_tc_model(const float *restrict x, const float *restrict g, float *restrict y,
+                                 int N, int C, int K, int H, int W, int mode) {
+  const int th = (H + 1) / 2, tw = (W + 1) / 2;
+  const int drop = mode == 1 ? 13 : 16;
+  float *U = (float *)malloc(sizeof(float) * (size_t)C * 16 * K);
+  oc_filter_transform(g, U, C, K);
+  if (mode) for (size_t i = 0; i < (size_t)C * 16 * K; ++i) U[i] = oc_round_bits(U[i], drop);
+#pragma omp parallel
+  {
+    float *V = (float *)aligned_alloc(64, sizeof(float) * 16 * (size_t)N);
+    double *M = (double *)aligned_alloc(64, sizeof(double) * 16 * (size_t)K * N);
+#pragma omp for collapse(2) schedule(dynamic, 1)
+    for (int ty = 0; ty < th; ++ty)
+      for (int tx = 0; tx < tw; ++tx) {
+        memset(M, 0, sizeof(double) * 16 * (size_t)K * N);
+        for (int c = 0; c < C; ++c) {
+          for (int n = 0; n < N; ++n) {
+            float d[16], b[16], v[16];
+            for (int i = 0; i < 4; ++i)
+              for (int j = 0; j < 4; ++j) {
+                int ih = 2 * ty - 1 + i, iw = 2 * tx - 1 + j;
+                d[4 * i + j] = (ih >= 0 && ih < H && iw >= 0 && iw < W)
+                                   ? x[(((size_t)c * H + ih) * W + iw) * N + n] : 0.0f;
+              }
+            for (int j = 0; j < 4; ++j) {
+              b[j] = d[j] - d[8 + j];
+              b[4 + j] = d[4 + j] + d[8 + j];
+              b[8 + j] = d[8 + j] - d[4 + j];
+              b[12 + j] = d[4 + j] - d[12 + j];
+            }
+            for (int i = 0; i < 4; ++i) {
+              v[4 * i + 0] = b[4 * i + 0] - b[4 * i + 2];
+              v[4 * i + 1] = b[4 * i + 1] + b[4 * i + 2];
+              v[4 * i + 2] = b[4 * i + 2] - b[4 * i + 1];
+              v[4 * i + 3] = b[4 * i + 1] - b[4 * i + 3];
+            }
+            for (int xi = 0; xi < 16; ++xi) V[xi * (size_t)N + n] = mode ? oc_round_bits(v[xi], drop) : v[xi];
+          }
+          for (int xi = 0; xi < 16; ++xi) {
+            const float *u = U + ((size_t)c * 16 + xi) * K;
+            const float *v = V + (size_t)xi * N;
+            for (int k = 0; k < K; ++k) {
+              double uk = (double)u[k];
+              double *m = M + ((size_t)xi * K + k) * N;
+              for (int n = 0; n < N; ++n) m[n] += (double)v[n] * uk;
+            }
+          }
+        }
+        for (int k = 0; k < K; ++k)
+          for (int n = 0; n < N; ++n) {
+            float m[16], a[8];
+            for (int xi = 0; xi < 16; ++xi) m[xi] = (float)M[((size_t)xi * K + k) * N + n];
+            for (int j = 0; j < 4; ++j) {
+              a[j] = m[j] + m[4 + j] + m[8 + j];
+              a[4 + j] = m[4 + j] - m[8 + j] - m[12 + j];
+            }
+            for (int i = 0; i < 2; ++i) {
+              int oh = 2 * ty + i;
+              if (oh >= H) continue;
+              float y0 = a[4 * i] + a[4 * i + 1] + a[4 * i + 2];
+              float y1 = a[4 * i + 1] - a[4 * i + 2] - a[4 * i + 3];
+              int ow = 2 * tx;
+              y[(((size_t)k * H + oh) * W + ow) * N + n] = y0;
+              if (ow + 1 < W) y[(((size_t)k * H + oh) * W + ow + 1) * N + n] = y1;
+            }
+          }
+      }
+    free(V);
+    free(M);
+  }
+  free(U);
+}
+
 /* Error statistics of a fp32 result against a fp64 truth; returns the number of elements with
  * |a-r| > rel * max(|r|, floor_) and writes max abs error, max|r| and rms(r). */
 OC_API int64_t oc_compare(const float *a, const double *r, size_t count, double rel, double floor_,

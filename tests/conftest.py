@@ -33,6 +33,7 @@ class Oracle:
         L.oc_filter_transform.argtypes = [f, f, ci, ci]
         L.oc_winograd_f32.argtypes = [f, f, f, ci, ci, ci, ci, ci]
         L.oc_convolution_forward.argtypes = [f, f, f, f, ci, ci, ci, ci, ci]
+        L.oc_winograd_tc_model.argtypes = [f, f, f, ci, ci, ci, ci, ci, ci]
         L.oc_round_tf32.argtypes = [f, ctypes.c_size_t]
         L.oc_round_bf16.argtypes = [f, ctypes.c_size_t]
         L.oc_num_threads.restype = ci
@@ -102,6 +103,14 @@ class Oracle:
 
     def forward(self, x, g):
         return self.winograd_f32(x, self.filter_transform(g))
+
+    def tc_model(self, x, g, precision):
+        """Model of the tensor-core path (operands rounded after the fp32 transforms)."""
+        C, H, W, N = x.shape
+        K = g.shape[3]
+        y = np.empty((K, H, W, N), np.float32)
+        self.L.oc_winograd_tc_model(self._p(x), self._p(g), self._p(y), N, C, K, H, W, {"tf32": 1, "bf16": 2}[precision])
+        return y
 
     def round_tf32(self, a):
         a = np.ascontiguousarray(a, np.float32).copy()

@@ -1,0 +1,60 @@
+"""The tcgen05 / TMEM path (TF32 and BF16 operands, fp32 accumulate) through the C ABI.
+
+Two checks per case: (1) against the CPU model of exactly that computation (fp32 transforms,
+operands rounded once, exact contraction) with a tight tolerance, which catches layout and
+indexing errors; (2) against the fp64 direct convolution with the tolerance the arithmetic
+allows, which is the accuracy claim of the path.  Inputs and filters are themselves rounded to
+the operand type first, as BASELINE's tensor-core configuration prescribes."""
+import numpy as np
+import pytest
+
+torch = pytest.importorskip("torch")
+
+from opencnn_b200 import api  # noqa: E402
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(32, 16, 128, 8, 8), (32, 8, 64, 7, 7), (64, 40, 192, 5, 9), (32, 64, 64, 14, 14), (96, 32, 256, 6, 6)]
+MODEL_REL = 2e-4                     # device vs model: fp32 accumulation order inside the tensor core
+TRUTH_REL = {"tf32": 4e-3, "bf16": 3e-2}   # device vs fp64 truth, relative to rms(truth)
+
+
+def run_tc(x, g, precision):
+    C, H, W, N = x.shape
+    K = g.shape[3]
+    dx, dg = torch.from_numpy(x).cuda(), torch.from_numpy(g).cuda()
+    dy = torch.full((K, H, W, N), float("nan"), device="cuda")
+    dws = torch.empty((C, 4, 4, K), device="cuda")
+    err = api.conv3x3(dx, dg, dy, dws, N, C, H, W, K, precision=precision,
+                      stream=torch.cuda.current_stream().cuda_stream)
+    assert err == 0, f"cudaError {err}"
+    assert api.last_device_status() == 0
+    return dy.cpu().numpy()
+
+
+@pytest.mark.parametrize("precision", ["tf32", "bf16"])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_tensor_core_path(oracle, libs, precision, shape):
+    N, C, K, H, W = shape
+    rnd = oracle.round_tf32 if precision == "tf32" else oracle.round_bf16
+    x = rnd(oracle.input_chwn(N, C, H, W)).reshape(C, H, W, N)
+    g = rnd(oracle.filter_crsk(C, K)).reshape(C, 3, 3, K)
+    y = run_tc(x, g, precision)
+    assert np.isfinite(y).all()
+    model = oracle.tc_model(x, g, precision)
+    rms = float(np.sqrt(np.mean(model.astype(np.float64) ** 2)))
+    worst = float(np.abs(y - model).max())
+    assert worst <= MODEL_REL * max(rms, 1e-30), f"vs model: {worst / rms:.3e} of rms"
+    truth = oracle.direct_f64(x, g)
+    trms = float(np.sqrt(np.mean(truth ** 2)))
+    tworst = float(np.abs(y - truth).max())
+    assert tworst <= TRUTH_REL[precision] * trms, f"vs fp64: {tworst / trms:.3e} of rms"
+
+
+@pytest.mark.parametrize("precision", ["tf32", "bf16"])
+def test_integer_tensors_are_exact_on_tensor_cores(oracle, libs, precision):
+    """Small integers are exact in both operand types and in the fp32 accumulator."""
+    N, C, K, H, W = 32, 16, 128, 6, 6
+    x, g = oracle.input_int(N, C, H, W), oracle.filter_int(C, K)
+    y = run_tc(x, g, precision)
+    assert np.array_equal(y.astype(np.float64), oracle.direct_f64(x, g))
