@@ -78,6 +78,20 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// True in exactly one lane of a fully converged warp.  Single-thread instructions that take their
+// operands from uniform registers (tcgen05.mma, TMA) are issued under this predicate by a warp
+// that executes the surrounding code convergently; issuing them from an `if (lane == 0)` branch
+// instead costs on the order of a hundred cycles per instruction.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xFFFFFFFF;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // Orders this thread's earlier generic-proxy shared-memory accesses before later async-proxy
 // (TMA) accesses to the same locations.
 __device__ __forceinline__ void fence_proxy_async_smem() {

@@ -20,19 +20,27 @@
 //   warps 1-4   input transform B^T d B in fp32, rounding, V written in the UMMA layout
 //   warp 5      MMA issue, tcgen05.commit to free stages and to publish a finished tile;
 //               also owns the TMEM allocation
-//   warps 6-9   epilogue: tcgen05.ld the 16 positions of (filter = TMEM lane, 4 images),
-//               A^T M A in registers - no shared-memory transpose - 16-byte stores
+//   warps 6-13  epilogue, two warps per TMEM lane quarter (each takes half of the 32 images):
+//               tcgen05.ld the 16 positions of (filter = TMEM lane, 4 images), A^T M A in
+//               registers - no shared-memory transpose - 16-byte stores
 // All hand-offs are mbarriers with bounded waits.
 #pragma once
 #include "fx.cuh"
 #include "ptx.cuh"
 #include "wino_fp32.cuh"   // WinoParams, TileCoord, output_transform, add2/sub2
 
+// Timing experiments only (never defined in shipped builds): bit 0 skips the U loads, bit 1 the
+// raw-input loads, bit 2 the input transform, bit 3 the MMAs, bit 4 the epilogue's loads/stores.
+#ifndef OCB_TC_ABLATE
+#define OCB_TC_ABLATE 0
+#endif
+
 namespace ocb {
 
 enum TcType : int { kTcBf16 = 0, kTcTf32 = 1 };
 
-constexpr int kTcThreads = 320;
+constexpr int kTcEpilogueWarps = 8;
+constexpr int kTcThreads = (6 + kTcEpilogueWarps) * 32;
 constexpr int kTcM = 128;                   // filters per CTA tile
 constexpr int kTcN = 32;                    // images per CTA tile
 constexpr int kTcStages = 2;
@@ -77,6 +85,11 @@ __device__ __forceinline__ void tmem_ld_x4(uint32_t taddr, float (&v)[4]) {
   asm volatile("tcgen05.ld.sync.aligned.32x32b.x4.b32 {%0, %1, %2, %3}, [%4];"
                : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(taddr) : "memory");
   v[0] = __uint_as_float(r0); v[1] = __uint_as_float(r1); v[2] = __uint_as_float(r2); v[3] = __uint_as_float(r3);
+}
+// 256-bit global store (one full 32-byte sector per lane); `p` must be 32-byte aligned.
+__device__ __forceinline__ void st_global_v8(float *p, const float (&a)[4], const float (&b)[4]) {
+  asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "f"(a[0]), "f"(a[1]), "f"(a[2]),
+               "f"(a[3]), "f"(b[0]), "f"(b[1]), "f"(b[2]), "f"(b[3]) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
@@ -225,7 +238,7 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
       mbar_init(smem_u32(uv_empty + s), 1);
     }
     mbar_init(smem_u32(acc_full), 1);
-    mbar_init(smem_u32(acc_empty), 4);
+    mbar_init(smem_u32(acc_empty), kTcEpilogueWarps);
     mbar_fence_init();
   }
   if (warp == 5) tmem_alloc_512(smem_u32(tmem_slot));
@@ -245,14 +258,22 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
         const int s = g % kTcStages;
         const uint32_t use = g / kTcStages;
         if (use > 0) mbar_wait(smem_u32(raw_empty + s), (use - 1) & 1, dead, p.status);
-        mbar_arrive_expect_tx(smem_u32(raw_full + s), Cfg::kRawBytes);
-        tma_load_4d(smem_u32(raw_s + s * Cfg::kRawBytes), &tm_in, smem_u32(raw_full + s), tc.nb * kTcN, 2 * tc.tx - 1,
-                    2 * tc.ty - 1, ci * KC);
+        if (OCB_TC_ABLATE & 2) {
+          mbar_arrive(smem_u32(raw_full + s));
+        } else {
+          mbar_arrive_expect_tx(smem_u32(raw_full + s), Cfg::kRawBytes);
+          tma_load_4d(smem_u32(raw_s + s * Cfg::kRawBytes), &tm_in, smem_u32(raw_full + s), tc.nb * kTcN, 2 * tc.tx - 1,
+                      2 * tc.ty - 1, ci * KC);
+        }
         if (use > 0) mbar_wait(smem_u32(uv_empty + s), (use - 1) & 1, dead, p.status);
-        mbar_arrive_expect_tx(smem_u32(u_full + s), kTcUBytes);
-        // U viewed as {filters within a 128-byte row, channel, 128-byte row of the filter axis, position}
-        tma_load_4d(smem_u32(u_s + s * kTcUBytes), &tm_u, smem_u32(u_full + s), 0, ci * KC,
-                    tc.kb * (DT == kTcBf16 ? 2 : 4), 0);
+        if (OCB_TC_ABLATE & 1) {
+          mbar_arrive(smem_u32(u_full + s));
+        } else {
+          mbar_arrive_expect_tx(smem_u32(u_full + s), kTcUBytes);
+          // U viewed as {filters within a 128-byte row, channel, 128-byte row of the filter axis, position}
+          tma_load_4d(smem_u32(u_s + s * kTcUBytes), &tm_u, smem_u32(u_full + s), 0, ci * KC,
+                      tc.kb * (DT == kTcBf16 ? 2 : 4), 0);
+        }
         if (++ci == cpt) {
           ci = 0;
           ++seq;
@@ -270,7 +291,8 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
       if (use > 0) mbar_wait(smem_u32(uv_empty + s), (use - 1) & 1, dead, p.status);   // V stage free again
       const float *raw = reinterpret_cast<const float *>(raw_s + s * Cfg::kRawBytes);
       uint8_t *vst = v_s + s * kTcVBytes;
-      if (DT == kTcBf16) {
+      if (OCB_TC_ABLATE & 4) {
+      } else if (DT == kTcBf16) {
         transform_to_v_bf16(raw, vst, t >> 4, t & 15);
         transform_to_v_bf16(raw, vst, (t >> 4) + 8, t & 15);
       } else {
@@ -286,8 +308,18 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
     }
   } else if (warp == 5) {
     // ===================================== MMA issuer ==========================================
+    // One thread issues.  Its instruction stream is the limit for these small MMAs (N = 32 costs
+    // the tensor pipe ~50 cycles), so the descriptors are built once and only advanced by
+    // constants inside the fully unrolled loop: building them per instruction made each MMA cost
+    // ~180 cycles.
     if (lane == 0) {
       const uint32_t idesc = instr_desc<DT>();
+      // A: 128 filters x KC channels, filter-contiguous rows of 128 B (64 bf16 / 32 tf32 filters), 8-channel
+      //    groups 1 KB apart, 128-byte-row blocks of the filter axis KC*128 B apart.
+      // B: 32 images x KC channels, image-contiguous rows (64 B bf16 / 128 B tf32), 8-channel groups 512 B apart.
+      // TF32 (32-bit, MN-major) uses the 128B-swizzle-with-32B-atom mode: 4-channel groups 512 B apart.
+      const uint64_t a_desc0 = DT == kTcBf16 ? smem_desc(smem_u32(u_s), KC * 128, 1024, 2) : smem_desc(smem_u32(u_s), KC * 128, 512, 1);
+      const uint64_t b_desc0 = DT == kTcBf16 ? smem_desc(smem_u32(v_s), 512, 512, 4) : smem_desc(smem_u32(v_s), 1024, 512, 1);
       int ci = 0, seq = 0;
       for (int g = 0; g < total_chunks; ++g) {
         const int s = g % kTcStages;
@@ -296,19 +328,11 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
         mbar_wait(smem_u32(v_ready + s), use & 1, dead, p.status);
         if (ci == 0 && seq > 0) mbar_wait(smem_u32(acc_empty), (seq - 1) & 1, dead, p.status);   // TMEM drained
         tc_fence_after();
-        const uint32_t ua = smem_u32(u_s + s * kTcUBytes), va = smem_u32(v_s + s * kTcVBytes);
-#pragma unroll 1
-        for (int xi = 0; xi < 16; ++xi) {
-          // A: 128 filters x KC channels, filter-contiguous rows of 128 B (64 bf16 / 32 tf32 filters), 8-channel
-          //    groups 1 KB apart, 128-byte-row blocks of the filter axis KC*128 B apart.
-          // B: 32 images x KC channels, image-contiguous rows (64 B bf16 / 128 B tf32), 8-channel groups 512 B apart.
-          // TF32 (32-bit, MN-major) uses the 128B-swizzle-with-32B-atom mode: 4-channel groups 512 B apart.
-          const uint64_t adesc = DT == kTcBf16 ? smem_desc(ua + xi * 4096, KC * 128, 1024, 2)
-                                               : smem_desc(ua + xi * 4096, KC * 128, 512, 1);
-          const uint64_t bdesc = DT == kTcBf16 ? smem_desc(va + xi * 1024, 512, 512, 4)
-                                               : smem_desc(va + xi * 1024, 1024, 512, 1);
-          tc_mma<DT>(tmem_base + xi * kTcN, adesc, bdesc, idesc, ci > 0 ? 1u : 0u);
-        }
+        const uint64_t ad = a_desc0 + (uint64_t)(s * (kTcUBytes >> 4)), bd = b_desc0 + (uint64_t)(s * (kTcVBytes >> 4));
+        const uint32_t accumulate = ci > 0 ? 1u : 0u;
+#pragma unroll
+        for (int xi = 0; xi < ((OCB_TC_ABLATE & 8) ? 0 : 16); ++xi)
+          tc_mma<DT>(tmem_base + xi * kTcN, ad + (uint64_t)(xi * (4096 >> 4)), bd + (uint64_t)(xi * (1024 >> 4)), idesc, accumulate);
         tc_commit(smem_u32(uv_empty + s));                 // stage reusable when these MMAs are done
         if (++ci == cpt) {
           tc_commit(smem_u32(acc_full));                   // tile finished
@@ -333,28 +357,41 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
       const bool row1 = (oh0 + 1) < p.H, col1 = (ow0 + 1) < p.W;
       float *ybase = p.y + (size_t)k * plane + ((size_t)oh0 * p.W + ow0) * p.N + (size_t)tc.nb * kTcN;
       const uint32_t tlane = tmem_base + ((uint32_t)(quarter * 32) << 16);
+      // Warps whose 32 filters all lie beyond K (K = 64 layers) have nothing to read or store.
+      const bool warp_valid = (tc.kb * kTcM + quarter * 32) < p.K;
+      // this warp's share of the 32 images: image quads jbase .. jbase + kIters - 1
+      constexpr int kIters = (OCB_TC_ABLATE & 16) ? 0 : (kTcN / 4) / (kTcEpilogueWarps / 4);
+      const int jbase = ((warp - 6) >> 2) * ((kTcN / 4) / (kTcEpilogueWarps / 4));
 #pragma unroll 1
-      for (int j = 0; j < kTcN / 4; ++j) {
-        float mm[16][4];
+      for (int jj = 0; jj < kIters; jj += 2) {
+        if (!warp_valid) break;
+        // Two image quads per step so that every store is one full 32-byte sector per lane: lanes
+        // are filters, i.e. different output rows, and 16-byte stores would touch twice the sectors.
+        float yq[2][4][4];                      // [quad][output position][image]
 #pragma unroll
-        for (int xi = 0; xi < 16; ++xi) tmem_ld_x4(tlane + xi * kTcN + 4 * j, mm[xi]);
-        tmem_ld_wait();
-        float y00[4], y01[4], y10[4], y11[4];
+        for (int h2 = 0; h2 < 2; ++h2) {
+          const int j = jbase + jj + h2;
+          float mm[16][4];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          float col[16], yy[4];
+          for (int xi = 0; xi < 16; ++xi) tmem_ld_x4(tlane + xi * kTcN + 4 * j, mm[xi]);
+          tmem_ld_wait();
 #pragma unroll
-          for (int xi = 0; xi < 16; ++xi) col[xi] = mm[xi][e];
-          output_transform(col, yy);
-          y00[e] = yy[0]; y01[e] = yy[1]; y10[e] = yy[2]; y11[e] = yy[3];
+          for (int e = 0; e < 4; ++e) {
+            float col[16], yy[4];
+#pragma unroll
+            for (int xi = 0; xi < 16; ++xi) col[xi] = mm[xi][e];
+            output_transform(col, yy);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) yq[h2][q][e] = yy[q];
+          }
         }
         if (valid) {
-          float *dst = ybase + 4 * j;
-          *reinterpret_cast<float4 *>(dst) = make_float4(y00[0], y00[1], y00[2], y00[3]);
-          if (col1) *reinterpret_cast<float4 *>(dst + dW) = make_float4(y01[0], y01[1], y01[2], y01[3]);
+          float *dst = ybase + 4 * (jbase + jj);
+          st_global_v8(dst, yq[0][0], yq[1][0]);
+          if (col1) st_global_v8(dst + dW, yq[0][1], yq[1][1]);
           if (row1) {
-            *reinterpret_cast<float4 *>(dst + dH) = make_float4(y10[0], y10[1], y10[2], y10[3]);
-            if (col1) *reinterpret_cast<float4 *>(dst + dH + dW) = make_float4(y11[0], y11[1], y11[2], y11[3]);
+            st_global_v8(dst + dH, yq[0][2], yq[1][2]);
+            if (col1) st_global_v8(dst + dH + dW, yq[0][3], yq[1][3]);
           }
         }
       }
