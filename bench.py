@@ -32,7 +32,9 @@ sys.path.insert(0, ROOT)
 LAYERS = [(128, 64, 64, 56), (128, 128, 128, 28), (128, 256, 256, 14), (128, 512, 512, 7)]  # N, C, K, H=W
 WORKLOAD = "resnet3x3_sweep_N128: (C=K=64,56x56) (128,28x28) (256,14x14) (512,7x7), stride 1, pad 1"
 METRIC = "effective TFLOP/s (direct-conv flops 2*N*K*C*H*W*9) over the N=128 ResNet 3x3 layer sweep"
-DRAM_TRAFFIC_PER_LAUNCH = None   # bytes, from the ncu capture summarised under profiles/
+# dram__bytes_read.sum + dram__bytes_write.sum per wino_fp32_kernel launch, averaged over the four
+# layers of one step: ncu capture of this very command at full size (profiles/bench_dram_traffic.md).
+DRAM_TRAFFIC_PER_LAUNCH = 81.05e6
 
 
 def direct_flops(N, C, K, HW):
@@ -157,6 +159,7 @@ def main():
     ap.add_argument("--precision", default="fp32", choices=["fp32", "tf32", "bf16"])
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-tensor-core", action="store_true", help="skip the extra TF32/BF16 measurements")
     ap.add_argument("--layers", default=None,
                     help="override the workload, e.g. '64,64,64,56;128,256,256,14' (N,C,K,H=W per layer); "
                          "for profiling small cases, not for reported numbers")
@@ -304,6 +307,46 @@ def main():
                         "over the sum of the four mean launch durations (CUDA events, this stream)",
                 "peak_source": peak_src,
                 "note": "the FFMA path is bound by the FP32 pipe, not by HBM or the tensor pipe"}
+    # ---- tensor-core path (additive option of the same operator; not the headline) ----------
+    tensor_core = None
+    if args.impl == "ours" and args.precision == "fp32" and not args.no_tensor_core:
+        peak_bf16, peak_src = 1590.0, "fallback 1.59 PFLOP/s (MEASURED_PEAKS.json absent)"
+        try:
+            mp = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+            peak_bf16, peak_src = float(mp["bf16_tflops"]), "MEASURED_PEAKS.json bf16_tflops (cuBLAS burst)"
+        except Exception:
+            pass
+        tensor_core = {"peak_bf16_tflops": peak_bf16, "peak_source": peak_src,
+                       "peak_tf32_tflops": peak_bf16 / 2, "peak_tf32_source": "half the bf16 figure (hardware rate ratio)"}
+        for prec in ("bf16", "tf32"):
+            reps_tc = 20
+            evs = [[(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True),
+                     torch.cuda.Event(enable_timing=True)) for _ in layers] for _ in range(reps_tc)]
+            for r in range(reps_tc):
+                for i, L in enumerate(layers):
+                    a, b, c = evs[r][i]
+                    a.record()
+                    api.filter_transform(L["g"], L["ws"], L["C"], L["K"], precision=prec, stream=stream, variant=args.variant)
+                    b.record()
+                    e = api.winograd_forward(L["x"], L["ws"], L["y"], L["N"], L["C"], L["HW"], L["HW"], L["K"],
+                                             precision=prec, stream=stream, variant=args.variant)
+                    c.record()
+                    if e != 0:
+                        raise RuntimeError(f"tensor-core path returned cudaError {e}")
+            torch.cuda.synchronize()
+            rows, tg, td, tt = [], 0.0, 0.0, 0.0
+            for i, L in enumerate(layers):
+                fx = statistics.mean(evs[r][i][0].elapsed_time(evs[r][i][1]) for r in range(3, reps_tc))
+                fu = statistics.mean(evs[r][i][1].elapsed_time(evs[r][i][2]) for r in range(3, reps_tc))
+                shp = (L["N"], L["C"], L["K"], L["HW"])
+                rows.append({"fx_us": fx * 1e3, "fused_us": fu * 1e3, "eff_tflops": direct_flops(*shp) / (fx + fu) * 1e-9,
+                             "gemm_tflops": gemm_flops(*shp) / fu * 1e-9})
+                tg += gemm_flops(*shp); td += direct_flops(*shp); tt += fx + fu
+            tf_fused = sum(r_["fused_us"] for r_ in rows) * 1e-6
+            pk = peak_bf16 if prec == "bf16" else peak_bf16 / 2
+            tensor_core[prec] = {"layers": rows, "eff_tflops": td / (tt * 1e-3) * 1e-12, "ms_per_step": tt,
+                                 "roofline": {"bound": "tensor", "kernel": "wino_tc_kernel", "achieved": tg / tf_fused * 1e-12,
+                                              "peak": pk, "unit": "TFLOP/s", "frac": tg / tf_fused * 1e-12 / pk}}
     clocks = sampler.stop()
 
     # ---- end to end with host buffers -------------------------------------------------------
@@ -382,6 +425,7 @@ def main():
             line["roofline"] = roof
             line["cpu_baseline"] = cb
             line["layers"] = per_layer
+            line["tensor_core"] = tensor_core
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()
