@@ -160,6 +160,7 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-tensor-core", action="store_true", help="skip the extra TF32/BF16 measurements")
+    ap.add_argument("--no-cudnn", action="store_true", help="skip the cuDNN (torch conv2d) baseline")
     ap.add_argument("--layers", default=None,
                     help="override the workload, e.g. '64,64,64,56;128,256,256,14' (N,C,K,H=W per layer); "
                          "for profiling small cases, not for reported numbers")
@@ -171,6 +172,7 @@ def main():
     if args.warmup < 3:
         args.warmup = 3
 
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")      # keep stdout for the one JSON line
     import torch
     import torch.distributed as dist
 
@@ -347,6 +349,32 @@ def main():
             tensor_core[prec] = {"layers": rows, "eff_tflops": td / (tt * 1e-3) * 1e-12, "ms_per_step": tt,
                                  "roofline": {"bound": "tensor", "kernel": "wino_tc_kernel", "achieved": tg / tf_fused * 1e-12,
                                               "peak": pk, "unit": "TFLOP/s", "frac": tg / tf_fused * 1e-12 / pk}}
+    # ---- cuDNN through torch (library baseline, NCHW tensors of the same shapes) ------------
+    cudnn = None
+    if args.impl == "ours" and world == 1 and not args.no_cudnn:
+        import torch.nn.functional as F
+        cudnn = {"how": "torch.nn.functional.conv2d, cudnn.benchmark=True, 20 timed calls per layer after 5 warm-ups; "
+                        "fp32 = TF32 disabled, NCHW; tf32 = TF32 allowed, channels_last", "version": torch.backends.cudnn.version()}
+        old = (torch.backends.cudnn.benchmark, torch.backends.cudnn.allow_tf32)
+        torch.backends.cudnn.benchmark = True
+        for name, tf32, fmt in (("fp32_nchw", False, torch.contiguous_format), ("tf32_channels_last", True, torch.channels_last)):
+            torch.backends.cudnn.allow_tf32 = tf32
+            us = []
+            for (N, C, K, HW) in LAYERS:
+                xx = torch.randn(N, C, HW, HW, device=dev).to(memory_format=fmt)
+                ww = (torch.randn(K, C, 3, 3, device=dev) * 0.05).to(memory_format=fmt)
+                for _ in range(5):
+                    F.conv2d(xx, ww, padding=1)
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for _ in range(20):
+                    F.conv2d(xx, ww, padding=1)
+                b.record()
+                torch.cuda.synchronize()
+                us.append(a.elapsed_time(b) * 1e3 / 20)
+                del xx, ww
+            cudnn[name] = {"us_per_layer": us, "eff_tflops": sum(direct_flops(*L) for L in LAYERS) / (sum(us) * 1e-6) * 1e-12}
+        torch.backends.cudnn.benchmark, torch.backends.cudnn.allow_tf32 = old
     clocks = sampler.stop()
 
     # ---- end to end with host buffers -------------------------------------------------------
@@ -426,6 +454,7 @@ def main():
             line["cpu_baseline"] = cb
             line["layers"] = per_layer
             line["tensor_core"] = tensor_core
+            line["cudnn"] = cudnn
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

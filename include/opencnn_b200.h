@@ -68,6 +68,14 @@ int opencnn_filter_transform_p(const float *filter, float *workspace, int in_c, 
 int opencnn_winograd_forward(const float *input, const float *workspace, float *output, int in_n, int in_c,
                              int in_h, int in_w, int filt_k, int precision, opencnn_stream_t stream);
 
+/* Layout adapters for callers that hold cuDNN-style tensors.  They replace data_cpy
+ * (src/openCNN_winograd.cu:147-153, launched :229-235), which scatters NCHW -> CHWN and
+ * KCRS -> CRSK one element per thread, and the index arithmetic with which the reference compares
+ * its KHWN output against an NCHW result (:185-186).  Dense fp32, src and dst must not overlap. */
+int opencnn_nchw_to_chwn(const float *src, float *dst, int n, int c, int h, int w, opencnn_stream_t stream);
+int opencnn_kcrs_to_crsk(const float *src, float *dst, int k, int c, opencnn_stream_t stream);
+int opencnn_khwn_to_nkhw(const float *src, float *dst, int n, int k, int h, int w, opencnn_stream_t stream);
+
 /* Bytes of workspace the operator needs: in_c*16*filt_k floats, as allocated by the reference's
  * caller (src/openCNN_winograd.cu:309-311). */
 size_t opencnn_workspace_bytes(int in_c, int filt_k);

@@ -24,6 +24,9 @@ SIGNATURES = {
     "opencnn_filter_transform_p": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "opencnn_winograd_forward": (c_int, [c_void_p] * 3 + [c_int] * 6 + [c_void_p]),
     "opencnn_convolutionForward_noalloc": (c_int, [c_void_p] * 3 + [c_int] * 5 + [c_void_p]),
+    "opencnn_nchw_to_chwn": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "opencnn_kcrs_to_crsk": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "opencnn_khwn_to_nkhw": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "opencnn_workspace_bytes": (c_size_t, [c_int, c_int]),
     "opencnn_variant_name": (c_char_p, []),
     "opencnn_last_device_status": (c_int, []),

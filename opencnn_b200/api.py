@@ -87,6 +87,18 @@ def winograd_forward(input_chwn, workspace, output_khwn, N, C, H, W, K, *, preci
                                                        H, W, K, PRECISIONS[precision], stream)
 
 
+def nchw_to_chwn(src, dst, N, C, H, W, *, stream=0, variant="OPTSTS64") -> int:
+    return _lib.load(variant).opencnn_nchw_to_chwn(_ptr(src), _ptr(dst), N, C, H, W, stream)
+
+
+def kcrs_to_crsk(src, dst, K, C, *, stream=0, variant="OPTSTS64") -> int:
+    return _lib.load(variant).opencnn_kcrs_to_crsk(_ptr(src), _ptr(dst), K, C, stream)
+
+
+def khwn_to_nkhw(src, dst, N, K, H, W, *, stream=0, variant="OPTSTS64") -> int:
+    return _lib.load(variant).opencnn_khwn_to_nkhw(_ptr(src), _ptr(dst), N, K, H, W, stream)
+
+
 def workspace_bytes(C, K, *, variant="OPTSTS64") -> int:
     return int(_lib.load(variant).opencnn_workspace_bytes(C, K))
 

@@ -11,6 +11,7 @@
 
 #include "../../include/opencnn_b200.h"
 #include "fx.cuh"
+#include "layout.cuh"
 #include "wino_fp32.cuh"
 #include "wino_tc.cuh"
 
@@ -348,6 +349,21 @@ int opencnn_convolutionForward_noalloc(const float *input, const float *filter, 
   e = launch_fx(filter, ws, in_c, filt_k, (cudaStream_t)stream);
   if (e != cudaSuccess) return (int)e;
   return (int)launch_wino_fp32(input, ws, output, in_n, in_c, in_h, in_w, filt_k, (cudaStream_t)stream);
+}
+
+int opencnn_nchw_to_chwn(const float *src, float *dst, int n, int c, int h, int w, opencnn_stream_t stream) {
+  if (n <= 0 || c <= 0 || h <= 0 || w <= 0) return (int)cudaErrorInvalidValue;
+  return (int)ocb::launch_transpose(src, dst, n, (long long)c * h * w, (cudaStream_t)stream);
+}
+
+int opencnn_kcrs_to_crsk(const float *src, float *dst, int k, int c, opencnn_stream_t stream) {
+  if (k <= 0 || c <= 0) return (int)cudaErrorInvalidValue;
+  return (int)ocb::launch_transpose(src, dst, k, (long long)c * 9, (cudaStream_t)stream);
+}
+
+int opencnn_khwn_to_nkhw(const float *src, float *dst, int n, int k, int h, int w, opencnn_stream_t stream) {
+  if (n <= 0 || k <= 0 || h <= 0 || w <= 0) return (int)cudaErrorInvalidValue;
+  return (int)ocb::launch_transpose(src, dst, (long long)k * h * w, n, (cudaStream_t)stream);
 }
 
 size_t opencnn_workspace_bytes(int in_c, int filt_k) {

@@ -16,7 +16,8 @@
 // Per K-step (16 channels in BF16, 8 in TF32) one elected thread issues 16 MMAs.
 //
 // Warp roles (320 threads):
-//   warp 0      TMA: raw input patches (4-D box, hardware zero-fill = halo) and U slices
+//   warp 0      TMA: raw input patches (4-D box, hardware zero-fill = halo)
+//   warp 14     TMA: U slices (a loader of its own, so patches never queue behind filter slices)
 //   warps 1-4   input transform B^T d B in fp32, rounding, V written in the UMMA layout
 //   warp 5      MMA issue, tcgen05.commit to free stages and to publish a finished tile;
 //               also owns the TMEM allocation
@@ -40,7 +41,7 @@ namespace ocb {
 enum TcType : int { kTcBf16 = 0, kTcTf32 = 1 };
 
 constexpr int kTcEpilogueWarps = 8;
-constexpr int kTcThreads = (6 + kTcEpilogueWarps) * 32;
+constexpr int kTcThreads = (6 + kTcEpilogueWarps + 1) * 32;   // + the U loader, last warp
 constexpr int kTcM = 128;                   // filters per CTA tile
 constexpr int kTcN = 32;                    // images per CTA tile
 constexpr int kTcStages = 2;
@@ -247,32 +248,38 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
-    // ===================================== TMA producer ========================================
+  if (warp == 0 || warp == kTcThreads / 32 - 1) {
+    // ===================================== TMA producers =======================================
+    // Two independent loaders, so that the input patches (needed early, by the transform) never
+    // wait behind the filter slices (whose stage is released late, by the MMAs): warp 0 loads the
+    // raw patches, the last warp loads U.
+    const bool loads_u = warp != 0;
     if (lane == 0) {
-      tma_prefetch_descriptor(&tm_in);
-      tma_prefetch_descriptor(&tm_u);
+      tma_prefetch_descriptor(loads_u ? &tm_u : &tm_in);
       int seq = 0, ci = 0;
       TileCoord tc = decode_tile(p, (int)blockIdx.x);
       for (int g = 0; g < total_chunks; ++g) {
         const int s = g % kTcStages;
         const uint32_t use = g / kTcStages;
-        if (use > 0) mbar_wait(smem_u32(raw_empty + s), (use - 1) & 1, dead, p.status);
-        if (OCB_TC_ABLATE & 2) {
-          mbar_arrive(smem_u32(raw_full + s));
+        if (!loads_u) {
+          if (use > 0) mbar_wait(smem_u32(raw_empty + s), (use - 1) & 1, dead, p.status);
+          if (OCB_TC_ABLATE & 2) {
+            mbar_arrive(smem_u32(raw_full + s));
+          } else {
+            mbar_arrive_expect_tx(smem_u32(raw_full + s), Cfg::kRawBytes);
+            tma_load_4d(smem_u32(raw_s + s * Cfg::kRawBytes), &tm_in, smem_u32(raw_full + s), tc.nb * kTcN,
+                        2 * tc.tx - 1, 2 * tc.ty - 1, ci * KC);
+          }
         } else {
-          mbar_arrive_expect_tx(smem_u32(raw_full + s), Cfg::kRawBytes);
-          tma_load_4d(smem_u32(raw_s + s * Cfg::kRawBytes), &tm_in, smem_u32(raw_full + s), tc.nb * kTcN, 2 * tc.tx - 1,
-                      2 * tc.ty - 1, ci * KC);
-        }
-        if (use > 0) mbar_wait(smem_u32(uv_empty + s), (use - 1) & 1, dead, p.status);
-        if (OCB_TC_ABLATE & 1) {
-          mbar_arrive(smem_u32(u_full + s));
-        } else {
-          mbar_arrive_expect_tx(smem_u32(u_full + s), kTcUBytes);
-          // U viewed as {filters within a 128-byte row, channel, 128-byte row of the filter axis, position}
-          tma_load_4d(smem_u32(u_s + s * kTcUBytes), &tm_u, smem_u32(u_full + s), 0, ci * KC,
-                      tc.kb * (DT == kTcBf16 ? 2 : 4), 0);
+          if (use > 0) mbar_wait(smem_u32(uv_empty + s), (use - 1) & 1, dead, p.status);
+          if (OCB_TC_ABLATE & 1) {
+            mbar_arrive(smem_u32(u_full + s));
+          } else {
+            mbar_arrive_expect_tx(smem_u32(u_full + s), kTcUBytes);
+            // U viewed as {filters within a 128-byte row, channel, 128-byte row of the filter axis, position}
+            tma_load_4d(smem_u32(u_s + s * kTcUBytes), &tm_u, smem_u32(u_full + s), 0, ci * KC,
+                        tc.kb * (DT == kTcBf16 ? 2 : 4), 0);
+          }
         }
         if (++ci == cpt) {
           ci = 0;
