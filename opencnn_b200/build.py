@@ -82,11 +82,28 @@ def build_peaks(force: bool = False) -> str:
     return target
 
 
+def smem_probe_lib_path() -> str:
+    return os.path.join(LIBDIR, "libopencnn_b200_smem_probe.so")
+
+
+def build_smem_probe(force: bool = False) -> str:
+    """The LDS/STS issue-rate probes (csrc/smem_probe.cu); not part of the operator."""
+    os.makedirs(LIBDIR, exist_ok=True)
+    target, src = smem_probe_lib_path(), os.path.join(CSRC, "smem_probe.cu")
+    if force or not os.path.exists(target) or os.path.getmtime(src) > os.path.getmtime(target):
+        cmd = [nvcc(), *ARCH, "-O3", "-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC", "-shared", "-o", target, src]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            raise RuntimeError(f"nvcc failed for smem_probe.cu:\n{res.stdout}\n{res.stderr}")
+    return target
+
+
 def build_all(force: bool = False, verbose: bool = False) -> list[str]:
-    with ThreadPoolExecutor(max_workers=5) as ex:
+    with ThreadPoolExecutor(max_workers=6) as ex:
         peaks = ex.submit(build_peaks, force)
+        probe = ex.submit(build_smem_probe, force)
         libs = list(ex.map(lambda v: build_variant(v, force, verbose), VARIANTS))
-        return libs + [peaks.result()]
+        return libs + [peaks.result(), probe.result()]
 
 
 if __name__ == "__main__":

@@ -55,13 +55,14 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
   return t;
 }
-
 // Waits for a phase of an mbarrier, but never for ever: after `limit_ns` of wall time (or as
 // soon as another thread of the CTA has given up) it sets the CTA's `dead` word and the global
 // status word and returns false.  The caller carries on with whatever is in shared memory, so
 // the kernel still terminates; the host sees the failure in the status word.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *dead, int *status,
                                           uint64_t limit_ns = 2000000000ull) {
+  // (Polling with the non-suspending test_wait first was measured and is slower: the spinning
+  // lanes take issue slots from the warps that do the work.)
   if (mbar_try_wait(bar, parity)) return true;
   if (*dead) return false;
   const uint64_t t0 = global_timer_ns();
