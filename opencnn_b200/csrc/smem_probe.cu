@@ -43,6 +43,13 @@ __device__ __forceinline__ uint32_t lane_offset(int pattern, int lane, int width
   }
 }
 
+// clock read that the compiler may not move across the volatile loads and stores
+__device__ __forceinline__ long long clock_now() {
+  long long t;
+  asm volatile("mov.u64 %0, %%clock64;" : "=l"(t)::"memory");
+  return t;
+}
+
 template <int OP>
 __global__ void __launch_bounds__(32, 1) smem_probe_kernel(long long *clocks, int pattern, float *sink) {
   __shared__ __align__(16) float buf[12288];
@@ -51,19 +58,19 @@ __global__ void __launch_bounds__(32, 1) smem_probe_kernel(long long *clocks, in
   constexpr int width = (OP == kLds32 || OP == kSts32) ? 4 : (OP == kLds64 || OP == kSts64) ? 8 : 16;
   const uint32_t addr = (uint32_t)__cvta_generic_to_shared(buf) + lane_offset(pattern, threadIdx.x, width);
   float a = 1.f, b = 2.f, c = 3.f, d = 4.f;
-  const long long t0 = clock64();
+  const long long t0 = clock_now();
   for (int outer = 0; outer < 128; ++outer) {
 #pragma unroll
     for (int i = 0; i < 128; ++i) {
-      if (OP == kLds32) asm volatile("ld.shared.f32 %0, [%1];" : "=f"(a) : "r"(addr));
-      if (OP == kLds64) asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(a), "=f"(b) : "r"(addr));
-      if (OP == kLds128) asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(a), "=f"(b), "=f"(c), "=f"(d) : "r"(addr));
-      if (OP == kSts32) asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(a) : "memory");
-      if (OP == kSts64) asm volatile("st.shared.v2.f32 [%0], {%1, %2};" ::"r"(addr), "f"(a), "f"(b) : "memory");
-      if (OP == kSts128) asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+      if (OP == kLds32) asm volatile("ld.volatile.shared.f32 %0, [%1];" : "=f"(a) : "r"(addr) : "memory");
+      if (OP == kLds64) asm volatile("ld.volatile.shared.v2.f32 {%0, %1}, [%2];" : "=f"(a), "=f"(b) : "r"(addr) : "memory");
+      if (OP == kLds128) asm volatile("ld.volatile.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(a), "=f"(b), "=f"(c), "=f"(d) : "r"(addr) : "memory");
+      if (OP == kSts32) asm volatile("st.volatile.shared.f32 [%0], %1;" ::"r"(addr), "f"(a) : "memory");
+      if (OP == kSts64) asm volatile("st.volatile.shared.v2.f32 [%0], {%1, %2};" ::"r"(addr), "f"(a), "f"(b) : "memory");
+      if (OP == kSts128) asm volatile("st.volatile.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
     }
   }
-  const long long t1 = clock64();
+  const long long t1 = clock_now();
   if (threadIdx.x == 0) clocks[0] = t1 - t0;
   sink[threadIdx.x] = a + b + c + d + buf[threadIdx.x];
 }
