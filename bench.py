@@ -157,7 +157,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--variant", default="OPTSTS64")
     ap.add_argument("--precision", default="fp32", choices=["fp32", "tf32", "bf16"])
-    ap.add_argument("--e2e-steps", type=int, default=10)
+    ap.add_argument("--e2e-steps", type=int, default=20)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-tensor-core", action="store_true", help="skip the extra TF32/BF16 measurements")
     ap.add_argument("--no-cudnn", action="store_true", help="skip the cuDNN (torch conv2d) baseline")
@@ -387,16 +387,29 @@ def main():
     h2d = sum(hx.numel() * 4 + hg.numel() * 4 for hx, hg, _ in host)
     d2h = sum(hy.numel() * 4 for _, _, hy in host)
     if args.impl == "ours":
-        plans = [api.HostPlan(L["N"], L["C"], L["HW"], L["HW"], L["K"], precision=args.precision, variant=args.variant)
-                 for L in layers]
+        # Two plans (device buffers + stream) and two host output buffers per layer, used alternately, so
+        # that the uploads of one step overlap the downloads of the step before (PCIe is full duplex).
+        # A plan is waited for before it is used again; the timed region ends after every step has landed.
+        plans = [[api.HostPlan(L["N"], L["C"], L["HW"], L["HW"], L["K"], precision=args.precision, variant=args.variant)
+                  for L in layers] for _ in range(2)]
+        host_out = [[hy for _, _, hy in host], [torch.empty(hy.shape, pin_memory=True) for _, _, hy in host]]
+        e2e_count = [0]
 
         def e2e_step():
-            for p, (hx, hg, hy) in zip(plans, host):
-                if p.run_async(hx.data_ptr(), hg.data_ptr(), hy.data_ptr()) != 0:
-                    raise RuntimeError("host plan failed")
-            for p in plans:
+            slot = e2e_count[0] & 1
+            e2e_count[0] += 1
+            for p in plans[slot]:                         # the step two back used this slot: its results must be home
                 if p.wait() != 0:
                     raise RuntimeError("host plan failed")
+            for p, (hx, hg, _), hy in zip(plans[slot], host, host_out[slot]):
+                if p.run_async(hx.data_ptr(), hg.data_ptr(), hy.data_ptr()) != 0:
+                    raise RuntimeError("host plan failed")
+
+        def e2e_drain():
+            for slot in (0, 1):
+                for p in plans[slot]:
+                    if p.wait() != 0:
+                        raise RuntimeError("host plan failed")
     else:
         def e2e_step():
             for L, (hx, hg, hy) in zip(layers, host):
@@ -405,22 +418,29 @@ def main():
                 run_layer(L)
                 hy.copy_(L["y"], non_blocking=True)
             torch.cuda.synchronize()
+
+        def e2e_drain():
+            torch.cuda.synchronize()
     for _ in range(3):
         e2e_step()
+    e2e_drain()
     sync_all()
     w0 = time.perf_counter()
     for _ in range(args.e2e_steps):
         e2e_step()
+    e2e_drain()
     torch.cuda.synchronize()
     e2e_ms = max_over_ranks((time.perf_counter() - w0) * 1e3) / args.e2e_steps
     e2e = {"value": flops_step / (e2e_ms * 1e-3) * 1e-12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
            "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": args.e2e_steps,
            "how": "pinned host buffers -> opencnn_host_plan_run_async per layer (H2D, FX, fused kernel, D2H on the "
-                  "plan's stream) -> wait on all four" if args.impl == "ours" else
+                  "plan's stream); two plan sets used alternately so uploads of a step overlap downloads of the "
+                  "previous one; every step's outputs are waited for inside the timed region" if args.impl == "ours" else
                   "pinned host buffers; per layer H2D, reference call, D2H on the default stream; one sync per step"}
     if args.impl == "ours":
-        for p in plans:
-            p.close()
+        for slot in plans:
+            for p in slot:
+                p.close()
         status = api.last_device_status(args.variant)
         if status != 0:
             raise RuntimeError(f"device status word = {status}: a bounded wait ran out; results invalid")
