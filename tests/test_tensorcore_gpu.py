@@ -14,7 +14,10 @@ from opencnn_b200 import api  # noqa: E402
 
 pytestmark = pytest.mark.gpu
 
-SHAPES = [(32, 16, 128, 8, 8), (32, 8, 64, 7, 7), (64, 40, 192, 5, 9), (32, 64, 64, 14, 14), (96, 32, 256, 6, 6)]
+# the last three have >= 32 K-steps per tile and >= 64 images: they take the CTA-pair kernel (also with an odd
+# number of 32-image blocks and with K not a multiple of 128); the others take the single-CTA kernel
+SHAPES = [(32, 16, 128, 8, 8), (32, 8, 64, 7, 7), (64, 40, 192, 5, 9), (32, 64, 64, 14, 14), (96, 32, 256, 6, 6),
+          (64, 512, 128, 4, 4), (96, 512, 192, 3, 5), (128, 520, 64, 2, 2)]
 MODEL_REL = 2e-4                     # device vs model: fp32 accumulation order inside the tensor core
 TRUTH_REL = {"tf32": 4e-3, "bf16": 3e-2}   # device vs fp64 truth, relative to rms(truth)
 
