@@ -448,10 +448,13 @@ wino_fp32_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constan
   constexpr int kLag = OCB_LAG;
   if (kLag > 0 && role.gi == 1 && total_chunks > kLag) mbar_wait(smem_u32(bar_ready + kLag), 0, dead, p.status);
 
-  Frag cur, nxt;
+  // Two operand buffers used alternately: channel c computes from frag[c & 1] while frag[(c + 1) & 1]
+  // is being loaded.  With the channel loop unrolled the indices are constants, so no register
+  // copies are needed (a "cur = nxt" hand-over cost 24 moves per channel).
+  Frag frag[2];
   if (total_chunks > 0) {
     mbar_wait(smem_u32(bar_ready + 0), 0, dead, p.status);
-    load_frag(cur, stages + voff, stages + uoff, o1, 0);
+    load_frag(frag[0], stages + voff, stages + uoff, o1, 0);
   }
   int ci = 0, seq = 0;
   for (int g = 0; g < total_chunks; ++g) {
@@ -460,7 +463,7 @@ wino_fp32_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constan
 #pragma unroll
     for (int c = 0; c < kBC; ++c) {
       if (c + 1 < kBC) {
-        load_frag(nxt, st + voff, st + uoff, o1, c + 1);
+        load_frag(frag[(c + 1) & 1], st + voff, st + uoff, o1, c + 1);
       } else {
         // all reads of this stage are done: hand it back, then look into the next one
         __syncwarp();
@@ -469,11 +472,10 @@ wino_fp32_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constan
           const int s1 = (g + 1) % S;
           mbar_wait(smem_u32(bar_ready + s1), ((g + 1) / S) & 1, dead, p.status);
           const float *st1 = stages + s1 * kStageFloats;
-          load_frag(nxt, st1 + voff, st1 + uoff, o1, 0);
+          load_frag(frag[0], st1 + voff, st1 + uoff, o1, 0);
         }
       }
-      fma_frag(acc, cur);
-      cur = nxt;
+      fma_frag(acc, frag[c & 1]);
     }
     if (++ci == cpt) {
       const TileCoord tc = decode_tile(p, (int)blockIdx.x + seq * (int)gridDim.x);
