@@ -173,6 +173,16 @@ cudaError_t launch_wino_fp32(const float *input, const float *workspace, float *
   p.chunks_per_tile = C / ocb::kBC;
   p.status = st->status_ptr;
   const int grid = p.total_tiles < st->sm_count ? p.total_tiles : st->sm_count;
+  // The last round of the persistent schedule is usually only partly filled.  If its tiles, cut in
+  // two (one item per consumer group), still fit on the SMs, cut them: that round then takes about
+  // half as long (see item_tile in wino_fp32.cuh).
+  const int full_rounds = p.total_tiles / grid, rest = p.total_tiles % grid;
+  p.split_from = p.total_tiles;
+  p.total_items = p.total_tiles;
+  if (rest > 0 && 2 * rest <= grid) {
+    p.split_from = full_rounds * grid;
+    p.total_items = p.split_from + 2 * rest;
+  }
   ocb::wino_fp32_kernel<OCB_VARIANT><<<grid, ocb::kThreads, ocb::SmemLayout<OCB_VARIANT>::kBytes, stream>>>(tm_in, tm_u, p);
   return cudaGetLastError();
 }
@@ -232,6 +242,7 @@ cudaError_t launch_wino_tc(const float *input, const float *workspace, float *ou
   const long long tiles = (long long)p.tiles_h * p.tiles_w * p.n_blocks * p.k_blocks;
   if (tiles > 0x7fffffffll / 8) return cudaErrorInvalidValue;
   p.total_tiles = (int)tiles;
+  p.split_from = p.total_items = p.total_tiles;
   p.chunks_per_tile = (C + KC - 1) / KC;
   p.status = st->status_ptr;
   const int grid = p.total_tiles < st->sm_count ? p.total_tiles : st->sm_count;
@@ -287,6 +298,7 @@ cudaError_t launch_wino_tc2(const float *input, const float *workspace, float *o
   const long long tiles = (long long)p.tiles_h * p.tiles_w * ((p.n_blocks + 1) / 2) * p.k_blocks;
   if (tiles > 0x7fffffffll / 8) return cudaErrorInvalidValue;
   p.total_tiles = (int)tiles;
+  p.split_from = p.total_items = p.total_tiles;
   p.chunks_per_tile = (C + KC - 1) / KC;
   p.status = st->status_ptr;
   const int clusters = p.total_tiles < max_clusters ? p.total_tiles : max_clusters;

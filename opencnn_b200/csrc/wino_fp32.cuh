@@ -90,6 +90,10 @@ struct WinoParams {
   float *y;            // output, KHWN
   int N, C, K, H, W;
   int tiles_h, tiles_w, n_blocks, k_blocks, total_tiles, chunks_per_tile;
+  // fp32 kernel only: work items.  Items below split_from are whole tiles; from there on each
+  // tile is two items, one per consumer group (see item_tile).  split_from == total_tiles and
+  // total_items == total_tiles mean "no split".
+  int split_from, total_items;
   int *status;         // device status word
 };
 
@@ -102,6 +106,21 @@ __device__ __forceinline__ TileCoord decode_tile(const WinoParams &p, int t) {
   tc.ty = t % p.tiles_h;
   tc.kb = t / p.tiles_h;
   return tc;
+}
+
+// Work item -> tile and the consumer groups that compute it (bit 0 = group 0, bit 1 = group 1).
+// The tiles of the last, partly filled round of the persistent schedule are cut in two items of 32
+// filters each and given to two SMs: a group that has the FMA pipe to itself runs almost twice as
+// fast, so that round takes about half as long.  The group that sits an item out only keeps the
+// ring moving (it hands every stage straight back).
+__device__ __forceinline__ int item_tile(const WinoParams &p, int item, int &groups) {
+  if (item < p.split_from) {
+    groups = 3;
+    return item;
+  }
+  const int j = item - p.split_from;
+  groups = 1 << (j & 1);
+  return p.split_from + (j >> 1);
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -361,7 +380,7 @@ wino_fp32_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constan
   volatile int *dead = reinterpret_cast<volatile int *>(bars + 3 * S);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int my_tiles = (p.total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
+  const int my_tiles = (p.total_items - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;   // work items
   const int cpt = p.chunks_per_tile;
   const int total_chunks = my_tiles * cpt;
 
@@ -384,8 +403,8 @@ wino_fp32_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constan
       if (lane == 0) {
         tma_prefetch_descriptor(&tm_in);
         tma_prefetch_descriptor(&tm_u);
-        int seq = 0, ci = 0;
-        TileCoord tc = decode_tile(p, (int)blockIdx.x);
+        int seq = 0, ci = 0, groups_unused;
+        TileCoord tc = decode_tile(p, item_tile(p, (int)blockIdx.x, groups_unused));
         for (int g = 0; g < total_chunks; ++g) {
           const int s = g % S;
           if (g >= S) mbar_wait(smem_u32(bar_empty + s), ((g / S) - 1) & 1, dead, p.status);
@@ -401,7 +420,7 @@ wino_fp32_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constan
           if (++ci == cpt) {
             ci = 0;
             ++seq;
-            if (seq < my_tiles) tc = decode_tile(p, (int)blockIdx.x + seq * (int)gridDim.x);
+            if (seq < my_tiles) tc = decode_tile(p, item_tile(p, (int)blockIdx.x + seq * (int)gridDim.x, groups_unused));
           }
         }
       }
@@ -454,31 +473,36 @@ wino_fp32_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constan
   Frag frag[2];
   if (total_chunks > 0) {
     mbar_wait(smem_u32(bar_ready + 0), 0, dead, p.status);
-    load_frag(frag[0], stages + voff, stages + uoff, o1, 0);
+    load_frag(frag[0], stages + voff, stages + uoff, o1, 0);   // harmless if this group sits the first item out
   }
-  int ci = 0, seq = 0;
-  for (int g = 0; g < total_chunks; ++g) {
-    const int s = g % S;
-    const float *st = stages + s * kStageFloats;
+  int g = 0;                                                       // chunk counter over all items of this CTA
+  for (int seq = 0; seq < my_tiles; ++seq) {
+    int groups;
+    const int tile = item_tile(p, (int)blockIdx.x + seq * (int)gridDim.x, groups);
+    if ((groups >> role.gi) & 1) {
+      // ---- this group computes the item ----
+      for (int ci = 0; ci < cpt; ++ci, ++g) {
+        const int s = g % S;
+        const float *st = stages + s * kStageFloats;
 #pragma unroll
-    for (int c = 0; c < kBC; ++c) {
-      if (c + 1 < kBC) {
-        load_frag(frag[(c + 1) & 1], st + voff, st + uoff, o1, c + 1);
-      } else {
-        // all reads of this stage are done: hand it back, then look into the next one
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(bar_empty + s));
-        if (g + 1 < total_chunks) {
-          const int s1 = (g + 1) % S;
-          mbar_wait(smem_u32(bar_ready + s1), ((g + 1) / S) & 1, dead, p.status);
-          const float *st1 = stages + s1 * kStageFloats;
-          load_frag(frag[0], st1 + voff, st1 + uoff, o1, 0);
+        for (int c = 0; c < kBC; ++c) {
+          if (c + 1 < kBC) {
+            load_frag(frag[(c + 1) & 1], st + voff, st + uoff, o1, c + 1);
+          } else {
+            // all reads of this stage are done: hand it back, then look into the next one
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(bar_empty + s));
+            if (g + 1 < total_chunks) {
+              const int s1 = (g + 1) % S;
+              mbar_wait(smem_u32(bar_ready + s1), ((g + 1) / S) & 1, dead, p.status);
+              const float *st1 = stages + s1 * kStageFloats;
+              load_frag(frag[0], st1 + voff, st1 + uoff, o1, 0);
+            }
+          }
+          fma_frag(acc, frag[c & 1]);
         }
       }
-      fma_frag(acc, frag[c & 1]);
-    }
-    if (++ci == cpt) {
-      const TileCoord tc = decode_tile(p, (int)blockIdx.x + seq * (int)gridDim.x);
+      const TileCoord tc = decode_tile(p, tile);
       if (!(OCB_ABLATE & 4)) {
         epilogue<V>(acc, my_stg, p, tc, role);
       } else {                                                    // keeps the accumulators alive
@@ -493,8 +517,19 @@ wino_fp32_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constan
       for (int a = 0; a < 8; ++a)
 #pragma unroll
         for (int b = 0; b < 8; ++b) acc[a][b] = 0ull;
-      ci = 0;
-      ++seq;
+    } else {
+      // ---- the other group computes it: only keep the ring moving, stage by stage ----
+      for (int ci = 0; ci < cpt; ++ci, ++g) {
+        const int s = g % S;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(bar_empty + s));
+        if (g + 1 < total_chunks) {
+          const int s1 = (g + 1) % S;
+          mbar_wait(smem_u32(bar_ready + s1), ((g + 1) / S) & 1, dead, p.status);
+          const float *st1 = stages + s1 * kStageFloats;
+          load_frag(frag[0], st1 + voff, st1 + uoff, o1, 0);       // in case the next item is ours
+        }
+      }
     }
   }
 }
