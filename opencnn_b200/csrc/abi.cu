@@ -76,6 +76,16 @@ cudaError_t device_state(DeviceState **out) {
     if (err == cudaSuccess)
       err = cudaFuncSetAttribute(ocb::wino_fp32_kernel<OCB_VARIANT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)ocb::SmemLayout<OCB_VARIANT>::kBytes);
+    if (err == cudaSuccess) {
+      // The kernel redistributes registers with setmaxnreg; that only works if the compiler gave
+      // the CTA at least the pool the budgets add up to.  Refuse to run a build where it did not
+      // (its consumer warps would wait for registers for ever).
+      cudaFuncAttributes fa;
+      err = cudaFuncGetAttributes(&fa, ocb::wino_fp32_kernel<OCB_VARIANT>);
+      if (err == cudaSuccess && fa.numRegs * ocb::kThreads < ocb::kConsumerThreads * ocb::kConsumerRegs +
+                                                                 ocb::kProducerThreads * ocb::kProducerRegs)
+        err = cudaErrorLaunchOutOfResources;
+    }
     if (err == cudaSuccess)
       err = cudaFuncSetAttribute(ocb::wino_tc_kernel<ocb::kTcBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)ocb::TcCfg<ocb::kTcBf16>::kSmemBytes);
@@ -270,7 +280,7 @@ cudaError_t launch_wino_tc2(const float *input, const float *workspace, float *o
   {
     cuuint64_t dims[4] = {(cuuint64_t)N, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)C};
     cuuint64_t strides[3] = {(cuuint64_t)N * 4, (cuuint64_t)W * N * 4, (cuuint64_t)H * W * N * 4};
-    cuuint32_t box[4] = {(cuuint32_t)ocb::kP2N, 4, 4, (cuuint32_t)KC};
+    cuuint32_t box[4] = {(cuuint32_t)ocb::kP2N, 4, 3, (cuuint32_t)KC};   // three patch rows per CTA
     cuuint32_t estr[4] = {1, 1, 1, 1};
     if (enc(&tm_in, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(input), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,

@@ -10,7 +10,8 @@
 //
 // The two CTAs of a pair run their main loops independently - each loads and transforms the raw
 // patches of all 64 images itself and keeps only its 8 positions (rows 2*rank, 2*rank+1 of the
-// 4x4 transform), so there is no cross-CTA traffic per K-step.  They meet only in the epilogue:
+// 4x4 transform), so there is no cross-CTA traffic per K-step.  Rows 0,1 of B^T d B need only
+// patch rows 0..2 and rows 2,3 only patch rows 1..3, so each CTA loads three of the four rows.  They meet only in the epilogue:
 // the output transform is linear in the 16 positions, so each CTA forms the partial result of its
 // 8 positions; CTA r stores its partial for image block r, signals the peer through an mbarrier in
 // the peer's shared memory, and for the other image block adds its partial onto what the peer
@@ -33,8 +34,10 @@ constexpr uint32_t kP2VBytes = 8 * 2048;         // 8 positions x (64 images x o
 
 template <int DT> struct P2Cfg {
   static constexpr int kKC = DT == kTcBf16 ? 16 : 8;
-  static constexpr uint32_t kRawBytes = kKC * 16 * kP2N * 4;          // [c][h][w][64 n] fp32
-  static constexpr size_t kSmemBytes = (size_t)kTcStages * (kRawBytes + kP2UBytes + kP2VBytes) + 1024;
+  static constexpr uint32_t kRawBytes = kKC * 12 * kP2N * 4;          // [c][3 h][4 w][64 n] fp32
+  // ring depth: what fits in 227 KB (BF16 stages are 96 KB, TF32 stages 72 KB)
+  static constexpr int kStages = DT == kTcBf16 ? 2 : 3;
+  static constexpr size_t kSmemBytes = (size_t)kStages * (kRawBytes + kP2UBytes + kP2VBytes) + 1024;
 };
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -61,29 +64,30 @@ __device__ __forceinline__ void red_global_add_v4(float *p, const float (&a)[4])
 // BF16: item = (channel c, image pair np of 32); V tile of a position is [16 c][64 n] bf16, rows of
 // 128 bytes, 128-byte swizzle.
 template <int RANK>
-__device__ __forceinline__ void p2_transform_bf16(const float *raw, uint8_t *vst, int c, int np) {
-  const uint64_t *R = reinterpret_cast<const uint64_t *>(raw + (c * 16) * kP2N + 2 * np);
+__device__ __forceinline__ void p2_transform_bf16(const float *__restrict__ raw, uint8_t *__restrict__ vst, int c, int np) {
+  const uint64_t *R = reinterpret_cast<const uint64_t *>(raw + (c * 12) * kP2N + 2 * np);
   constexpr int P = kP2N / 2;
-  uint64_t d[16], b[16];
+  uint64_t d[12], b[8];                      // d: patch rows RANK..RANK+2; b: transform rows 2*RANK, 2*RANK+1
 #pragma unroll
-  for (int q = 0; q < 16; ++q) d[q] = R[q * P];
+  for (int q = 0; q < 12; ++q) d[q] = R[q * P];
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    b[j] = sub2(d[j], d[8 + j]);
-    b[4 + j] = add2(d[4 + j], d[8 + j]);
-    b[8 + j] = sub2(d[8 + j], d[4 + j]);
-    b[12 + j] = sub2(d[4 + j], d[12 + j]);
+    if (RANK == 0) {
+      b[j] = sub2(d[j], d[8 + j]);           // row 0 = d0 - d2
+      b[4 + j] = add2(d[4 + j], d[8 + j]);   // row 1 = d1 + d2
+    } else {
+      b[j] = sub2(d[4 + j], d[j]);           // row 2 = d2 - d1
+      b[4 + j] = sub2(d[j], d[8 + j]);       // row 3 = d1 - d3
+    }
   }
   uint8_t *dst = vst + c * 128 + ((((np >> 2) ^ c) & 7) << 4) + ((np & 3) << 2);
 #pragma unroll
   for (int ii = 0; ii < 2; ++ii) {
-    constexpr int base = 2 * RANK;
-    const int i = base + ii;
     uint64_t o[4];
-    o[0] = sub2(b[4 * i + 0], b[4 * i + 2]);
-    o[1] = add2(b[4 * i + 1], b[4 * i + 2]);
-    o[2] = sub2(b[4 * i + 2], b[4 * i + 1]);
-    o[3] = sub2(b[4 * i + 1], b[4 * i + 3]);
+    o[0] = sub2(b[4 * ii + 0], b[4 * ii + 2]);
+    o[1] = add2(b[4 * ii + 1], b[4 * ii + 2]);
+    o[2] = sub2(b[4 * ii + 2], b[4 * ii + 1]);
+    o[3] = sub2(b[4 * ii + 1], b[4 * ii + 3]);
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       float lo, hi;
@@ -95,29 +99,30 @@ __device__ __forceinline__ void p2_transform_bf16(const float *raw, uint8_t *vst
 // TF32: item = (channel c, image n of 64); V tile of a position is [2 image blocks][8 c][32 n] fp32,
 // rows of 128 bytes, 128-byte swizzle with 32-byte atoms.
 template <int RANK>
-__device__ __forceinline__ void p2_transform_tf32(const float *raw, uint8_t *vst, int c, int n) {
-  const float *R = raw + (c * 16) * kP2N + n;
-  float d[16], b[16];
+__device__ __forceinline__ void p2_transform_tf32(const float *__restrict__ raw, uint8_t *__restrict__ vst, int c, int n) {
+  const float *R = raw + (c * 12) * kP2N + n;
+  float d[12], b[8];
 #pragma unroll
-  for (int q = 0; q < 16; ++q) d[q] = R[q * kP2N];
+  for (int q = 0; q < 12; ++q) d[q] = R[q * kP2N];
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    b[j] = __fsub_rn(d[j], d[8 + j]);
-    b[4 + j] = __fadd_rn(d[4 + j], d[8 + j]);
-    b[8 + j] = __fsub_rn(d[8 + j], d[4 + j]);
-    b[12 + j] = __fsub_rn(d[4 + j], d[12 + j]);
+    if (RANK == 0) {
+      b[j] = __fsub_rn(d[j], d[8 + j]);
+      b[4 + j] = __fadd_rn(d[4 + j], d[8 + j]);
+    } else {
+      b[j] = __fsub_rn(d[4 + j], d[j]);
+      b[4 + j] = __fsub_rn(d[j], d[8 + j]);
+    }
   }
   const int nl = n & 31;
   uint8_t *dst = vst + (n >> 5) * 1024 + c * 128 + ((((nl >> 3) ^ c) & 3) << 5) + ((nl & 7) << 2);
 #pragma unroll
   for (int ii = 0; ii < 2; ++ii) {
-    constexpr int base = 2 * RANK;
-    const int i = base + ii;
     float o[4];
-    o[0] = __fsub_rn(b[4 * i + 0], b[4 * i + 2]);
-    o[1] = __fadd_rn(b[4 * i + 1], b[4 * i + 2]);
-    o[2] = __fsub_rn(b[4 * i + 2], b[4 * i + 1]);
-    o[3] = __fsub_rn(b[4 * i + 1], b[4 * i + 3]);
+    o[0] = __fsub_rn(b[4 * ii + 0], b[4 * ii + 2]);
+    o[1] = __fadd_rn(b[4 * ii + 1], b[4 * ii + 2]);
+    o[2] = __fsub_rn(b[4 * ii + 2], b[4 * ii + 1]);
+    o[3] = __fsub_rn(b[4 * ii + 1], b[4 * ii + 3]);
 #pragma unroll
     for (int j = 0; j < 4; ++j) *reinterpret_cast<float *>(dst + (4 * ii + j) * 2048) = round_tf32_rne(o[j]);
   }
@@ -155,14 +160,15 @@ __device__ __forceinline__ void p2_body(const CUtensorMap &tm_in, const CUtensor
                                         uint8_t *tsmem) {
   using Cfg = P2Cfg<DT>;
   constexpr int KC = Cfg::kKC;
+  constexpr int S = Cfg::kStages;
   uint8_t *raw_s = tsmem;
-  uint8_t *u_s = raw_s + kTcStages * Cfg::kRawBytes;
-  uint8_t *v_s = u_s + kTcStages * kP2UBytes;
-  uint64_t *bars = reinterpret_cast<uint64_t *>(v_s + kTcStages * kP2VBytes);
-  uint64_t *raw_full = bars, *raw_empty = bars + 2, *u_full = bars + 4, *v_ready = bars + 6, *uv_empty = bars + 8;
-  uint64_t *acc_full = bars + 10, *acc_empty = bars + 11, *peer_ready = bars + 12;   // peer_ready[2], used alternately
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 14);
-  volatile int *dead = reinterpret_cast<volatile int *>(bars + 15);
+  uint8_t *u_s = raw_s + S * Cfg::kRawBytes;
+  uint8_t *v_s = u_s + S * kP2UBytes;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(v_s + S * kP2VBytes);
+  uint64_t *raw_full = bars, *raw_empty = bars + S, *u_full = bars + 2 * S, *v_ready = bars + 3 * S, *uv_empty = bars + 4 * S;
+  uint64_t *acc_full = bars + 5 * S, *acc_empty = acc_full + 1, *peer_ready = acc_full + 2;   // peer_ready[2], used alternately
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 4);
+  volatile int *dead = reinterpret_cast<volatile int *>(acc_full + 5);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_clusters = (int)gridDim.x / 2, cid = (int)blockIdx.x / 2;
@@ -173,14 +179,15 @@ __device__ __forceinline__ void p2_body(const CUtensorMap &tm_in, const CUtensor
 
   if (tid == 0) {
     *dead = 0;
-    for (int s = 0; s < kTcStages; ++s) {
+    for (int s = 0; s < S; ++s) {
       mbar_init(smem_u32(raw_full + s), 1);
       mbar_init(smem_u32(raw_empty + s), kP2TransformWarps);
       mbar_init(smem_u32(u_full + s), 1);
       mbar_init(smem_u32(v_ready + s), kP2TransformWarps);
       mbar_init(smem_u32(uv_empty + s), 1);
-      mbar_init(smem_u32(peer_ready + s), kP2EpilogueWarps);
     }
+    mbar_init(smem_u32(peer_ready + 0), kP2EpilogueWarps);
+    mbar_init(smem_u32(peer_ready + 1), kP2EpilogueWarps);
     mbar_init(smem_u32(acc_full), 1);
     mbar_init(smem_u32(acc_empty), kP2EpilogueWarps);
     mbar_fence_init();
@@ -200,13 +207,13 @@ __device__ __forceinline__ void p2_body(const CUtensorMap &tm_in, const CUtensor
       int seq = 0, ci = 0;
       P2Tile tc = p2_decode(p, cid, n_pairs);
       for (int g = 0; g < total_chunks; ++g) {
-        const int s = g % kTcStages;
-        const uint32_t use = g / kTcStages;
+        const int s = g % S;
+        const uint32_t use = g / S;
         if (!loads_u) {
           if (use > 0) mbar_wait(smem_u32(raw_empty + s), (use - 1) & 1, dead, p.status);
           mbar_arrive_expect_tx(smem_u32(raw_full + s), Cfg::kRawBytes);
           tma_load_4d(smem_u32(raw_s + s * Cfg::kRawBytes), &tm_in, smem_u32(raw_full + s), tc.np * kP2N, 2 * tc.tx - 1,
-                      2 * tc.ty - 1, ci * KC);
+                      2 * tc.ty - 1 + RANK, ci * KC);           // patch rows RANK .. RANK+2
         } else {
           if (use > 0) mbar_wait(smem_u32(uv_empty + s), (use - 1) & 1, dead, p.status);
           mbar_arrive_expect_tx(smem_u32(u_full + s), kP2UBytes);
@@ -224,12 +231,12 @@ __device__ __forceinline__ void p2_body(const CUtensorMap &tm_in, const CUtensor
     // ===================================== input transform =====================================
     const int t = tid - 32;                                            // 0..255
     for (int g = 0; g < total_chunks; ++g) {
-      const int s = g % kTcStages;
-      const uint32_t use = g / kTcStages;
+      const int s = g % S;
+      const uint32_t use = g / S;
       mbar_wait(smem_u32(raw_full + s), use & 1, dead, p.status);
       if (use > 0) mbar_wait(smem_u32(uv_empty + s), (use - 1) & 1, dead, p.status);   // V stage free again
-      const float *raw = reinterpret_cast<const float *>(raw_s + s * Cfg::kRawBytes);
-      uint8_t *vst = v_s + s * kP2VBytes;
+      const float *__restrict__ raw = reinterpret_cast<const float *>(raw_s + s * Cfg::kRawBytes);
+      uint8_t *__restrict__ vst = v_s + s * kP2VBytes;
       if (DT == kTcBf16) {
         p2_transform_bf16<RANK>(raw, vst, t >> 5, t & 31);
         p2_transform_bf16<RANK>(raw, vst, (t >> 5) + 8, t & 31);
@@ -256,8 +263,8 @@ __device__ __forceinline__ void p2_body(const CUtensorMap &tm_in, const CUtensor
       const uint64_t b_desc0 = DT == kTcBf16 ? smem_desc(smem_u32(v_s), 1024, 1024, 2) : smem_desc(smem_u32(v_s), 1024, 512, 1);
       int ci = 0, seq = 0;
       for (int g = 0; g < total_chunks; ++g) {
-        const int s = g % kTcStages;
-        const uint32_t use = g / kTcStages;
+        const int s = g % S;
+        const uint32_t use = g / S;
         mbar_wait(smem_u32(u_full + s), use & 1, dead, p.status);
         mbar_wait(smem_u32(v_ready + s), use & 1, dead, p.status);
         if (ci == 0 && seq > 0) mbar_wait(smem_u32(acc_empty), (seq - 1) & 1, dead, p.status);   // TMEM drained
