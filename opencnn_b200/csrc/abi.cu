@@ -124,9 +124,17 @@ cudaError_t device_state(DeviceState **out) {
 
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-cudaError_t check_shape(int N, int C, int H, int W, int K) {
+// `n_multiple`: what the batch must be a multiple of.  The two legacy entry points keep the
+// reference's rule (32).  The other entries accept a ragged last block of images: 4 on the fp32
+// path (rows of the tensors must stay 16-byte aligned for TMA), 8 on the tensor-core path (its
+// epilogue stores eight images per lane).  Loads of the missing images are zero-filled by TMA,
+// their outputs are not stored.
+constexpr int kLegacyBatchMultiple = 32;
+int batch_multiple(int precision) { return precision == OPENCNN_FP32 ? 4 : 8; }
+
+cudaError_t check_shape(int N, int C, int H, int W, int K, int n_multiple) {
   if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || K <= 0) return cudaErrorInvalidValue;
-  if (N % ocb::kBN || K % ocb::kBK || C % ocb::kBC) return cudaErrorInvalidValue;
+  if (N % n_multiple || K % ocb::kBK || C % ocb::kBC) return cudaErrorInvalidValue;
   // 32-bit tile arithmetic and TMA extents
   if ((long long)N * C * H * W >= (1ll << 40) || (long long)N * K * H * W >= (1ll << 40)) return cudaErrorInvalidValue;
   return cudaSuccess;
@@ -175,7 +183,7 @@ cudaError_t launch_wino_fp32(const float *input, const float *workspace, float *
   p.N = N; p.C = C; p.K = K; p.H = H; p.W = W;
   p.tiles_h = (H + 1) / 2;
   p.tiles_w = (W + 1) / 2;
-  p.n_blocks = N / ocb::kBN;
+  p.n_blocks = (N + ocb::kBN - 1) / ocb::kBN;
   p.k_blocks = K / ocb::kBK;
   const long long tiles = (long long)p.tiles_h * p.tiles_w * p.n_blocks * p.k_blocks;
   if (tiles > 0x7fffffffll / 8) return cudaErrorInvalidValue;
@@ -247,7 +255,7 @@ cudaError_t launch_wino_tc(const float *input, const float *workspace, float *ou
   p.N = N; p.C = C; p.K = K; p.H = H; p.W = W;
   p.tiles_h = (H + 1) / 2;
   p.tiles_w = (W + 1) / 2;
-  p.n_blocks = N / ocb::kTcN;
+  p.n_blocks = (N + ocb::kTcN - 1) / ocb::kTcN;
   p.k_blocks = (K + ocb::kTcM - 1) / ocb::kTcM;
   const long long tiles = (long long)p.tiles_h * p.tiles_w * p.n_blocks * p.k_blocks;
   if (tiles > 0x7fffffffll / 8) return cudaErrorInvalidValue;
@@ -303,7 +311,7 @@ cudaError_t launch_wino_tc2(const float *input, const float *workspace, float *o
   p.N = N; p.C = C; p.K = K; p.H = H; p.W = W;
   p.tiles_h = (H + 1) / 2;
   p.tiles_w = (W + 1) / 2;
-  p.n_blocks = N / ocb::kTcN;
+  p.n_blocks = (N + ocb::kTcN - 1) / ocb::kTcN;
   p.k_blocks = (K + ocb::kTcM - 1) / ocb::kTcM;
   const long long tiles = (long long)p.tiles_h * p.tiles_w * ((p.n_blocks + 1) / 2) * p.k_blocks;
   if (tiles > 0x7fffffffll / 8) return cudaErrorInvalidValue;
@@ -335,10 +343,11 @@ cudaError_t launch_tc(const float *input, const float *workspace, float *output,
 }
 
 cudaError_t forward(const float *input, const float *filter, float *output, float *workspace, int N, int C, int H,
-                    int W, int K, int precision, cudaStream_t stream) {
+                    int W, int K, int precision, cudaStream_t stream, int n_multiple) {
   if (!input || !filter || !output || !workspace) return cudaErrorInvalidValue;
   if (!aligned16(input) || !aligned16(filter) || !aligned16(output) || !aligned16(workspace)) return cudaErrorInvalidValue;
-  cudaError_t e = check_shape(N, C, H, W, K);
+  if (precision != OPENCNN_FP32 && precision != OPENCNN_TF32 && precision != OPENCNN_BF16) return cudaErrorInvalidValue;
+  cudaError_t e = check_shape(N, C, H, W, K, n_multiple);
   if (e != cudaSuccess) return e;
   if (precision == OPENCNN_BF16) {
     e = launch_fx_tc<ocb::kTcBf16>(filter, workspace, C, K, stream);
@@ -403,7 +412,7 @@ int convolutionForward_32x64x8(float *k, int in_h, int in_w, float *w, int out_h
   if (filt_c != in_c || out_c != filt_k || out_n != in_n || out_h != in_h || out_w != in_w)
     return (int)cudaErrorInvalidValue;
   if (tiles_dim != (in_w + 1) / 2) return (int)cudaErrorInvalidValue;
-  return (int)forward(k, w, C, Ww, in_n, in_c, in_h, in_w, filt_k, OPENCNN_FP32, (cudaStream_t)0);
+  return (int)forward(k, w, C, Ww, in_n, in_c, in_h, in_w, filt_k, OPENCNN_FP32, (cudaStream_t)0, kLegacyBatchMultiple);
 }
 
 int convolutionForward(float *k, int in_h, int in_w, float *w, int out_h, int out_w, int out_n, int out_c,
@@ -419,7 +428,7 @@ int opencnn_convolutionForward_stream(const float *input, const float *filter, f
                                       int in_n, int in_c, int in_h, int in_w, int filt_k, int precision,
                                       opencnn_stream_t stream) {
   return (int)forward(input, filter, output, workspace, in_n, in_c, in_h, in_w, filt_k, precision,
-                      (cudaStream_t)stream);
+                      (cudaStream_t)stream, batch_multiple(precision));
 }
 
 int opencnn_filter_transform(const float *filter, float *workspace, int in_c, int filt_k, opencnn_stream_t stream) {
@@ -440,7 +449,8 @@ int opencnn_winograd_forward(const float *input, const float *workspace, float *
                              int in_h, int in_w, int filt_k, int precision, opencnn_stream_t stream) {
   if (!input || !workspace || !output) return (int)cudaErrorInvalidValue;
   if (!aligned16(input) || !aligned16(workspace) || !aligned16(output)) return (int)cudaErrorInvalidValue;
-  cudaError_t e = check_shape(in_n, in_c, in_h, in_w, filt_k);
+  if (precision != OPENCNN_FP32 && precision != OPENCNN_TF32 && precision != OPENCNN_BF16) return (int)cudaErrorInvalidValue;
+  cudaError_t e = check_shape(in_n, in_c, in_h, in_w, filt_k, batch_multiple(precision));
   if (e != cudaSuccess) return (int)e;
   if (precision == OPENCNN_BF16)
     return (int)launch_tc<ocb::kTcBf16>(input, workspace, output, in_n, in_c, in_h, in_w, filt_k, (cudaStream_t)stream);
@@ -454,7 +464,7 @@ int opencnn_convolutionForward_noalloc(const float *input, const float *filter, 
                                        int in_c, int in_h, int in_w, int filt_k, opencnn_stream_t stream) {
   if (!input || !filter || !output) return (int)cudaErrorInvalidValue;
   if (!aligned16(input) || !aligned16(filter) || !aligned16(output)) return (int)cudaErrorInvalidValue;
-  cudaError_t e = check_shape(in_n, in_c, in_h, in_w, filt_k);
+  cudaError_t e = check_shape(in_n, in_c, in_h, in_w, filt_k, batch_multiple(OPENCNN_FP32));
   if (e != cudaSuccess) return (int)e;
   if ((long long)in_c * filt_k > (long long)OPENCNN_NOALLOC_MAX_CK) {
     std::fprintf(stderr,
@@ -505,9 +515,9 @@ int opencnn_last_device_status(void) {
 int opencnn_host_plan_create(void **plan, int in_n, int in_c, int in_h, int in_w, int filt_k, int precision) {
   if (!plan) return (int)cudaErrorInvalidValue;
   *plan = nullptr;
-  cudaError_t e = check_shape(in_n, in_c, in_h, in_w, filt_k);
-  if (e != cudaSuccess) return (int)e;
   if (precision != OPENCNN_FP32 && precision != OPENCNN_TF32 && precision != OPENCNN_BF16) return (int)cudaErrorInvalidValue;
+  cudaError_t e = check_shape(in_n, in_c, in_h, in_w, filt_k, batch_multiple(precision));
+  if (e != cudaSuccess) return (int)e;
   HostPlan *hp = new (std::nothrow) HostPlan;
   if (!hp) return (int)cudaErrorMemoryAllocation;
   hp->N = in_n; hp->C = in_c; hp->H = in_h; hp->W = in_w; hp->K = filt_k; hp->precision = precision;
@@ -535,7 +545,8 @@ int opencnn_host_plan_run_async(void *plan, const float *input_host, const float
   cudaError_t e = cudaMemcpyAsync(hp->d_filt, filter_host, f_b, cudaMemcpyHostToDevice, hp->stream);
   if (e == cudaSuccess) e = cudaMemcpyAsync(hp->d_in, input_host, in_b, cudaMemcpyHostToDevice, hp->stream);
   if (e == cudaSuccess)
-    e = forward(hp->d_in, hp->d_filt, hp->d_out, hp->d_ws, hp->N, hp->C, hp->H, hp->W, hp->K, hp->precision, hp->stream);
+    e = forward(hp->d_in, hp->d_filt, hp->d_out, hp->d_ws, hp->N, hp->C, hp->H, hp->W, hp->K, hp->precision, hp->stream,
+                batch_multiple(hp->precision));
   if (e == cudaSuccess) e = cudaMemcpyAsync(output_host, hp->d_out, out_b, cudaMemcpyDeviceToHost, hp->stream);
   return (int)e;
 }

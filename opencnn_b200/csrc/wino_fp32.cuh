@@ -197,6 +197,10 @@ __device__ __forceinline__ void epilogue(uint64_t (&acc)[8][8], float *stg, cons
   float *ybase = p.y + ((size_t)oh0 * p.W + ow0) * p.N + (size_t)tc.nb * kBN +
                  ((size_t)tc.kb * kBK + 32 * role.gi) * plane;
   const size_t dW = (size_t)p.N, dH = (size_t)p.W * p.N;
+  // Ragged last image block (N not a multiple of 32): the missing images were loaded as zeros and
+  // are not stored.  N is a multiple of 4, so an image pair is either inside or outside.
+  const int n_left = p.N - tc.nb * kBN;
+  const bool n_ok = (V == kOptLds64 ? 2 * (lane & 15) : lane) < n_left;
 
 #pragma unroll
   for (int r = 0; r < 4; ++r) {
@@ -236,11 +240,13 @@ __device__ __forceinline__ void epilogue(uint64_t (&acc)[8][8], float *stg, cons
       output_transform(m0, y0);
       output_transform(m1, y1);
       float *dst = ybase + (size_t)round_filter<V>(kl, r) * plane + 2 * np;
-      *reinterpret_cast<float2 *>(dst) = make_float2(y0[0], y1[0]);
-      if (col1) *reinterpret_cast<float2 *>(dst + dW) = make_float2(y0[1], y1[1]);
-      if (row1) {
-        *reinterpret_cast<float2 *>(dst + dH) = make_float2(y0[2], y1[2]);
-        if (col1) *reinterpret_cast<float2 *>(dst + dH + dW) = make_float2(y0[3], y1[3]);
+      if (n_ok) {
+        *reinterpret_cast<float2 *>(dst) = make_float2(y0[0], y1[0]);
+        if (col1) *reinterpret_cast<float2 *>(dst + dW) = make_float2(y0[1], y1[1]);
+        if (row1) {
+          *reinterpret_cast<float2 *>(dst + dH) = make_float2(y0[2], y1[2]);
+          if (col1) *reinterpret_cast<float2 *>(dst + dH + dW) = make_float2(y0[3], y1[3]);
+        }
       }
     } else {
 #pragma unroll
@@ -256,11 +262,13 @@ __device__ __forceinline__ void epilogue(uint64_t (&acc)[8][8], float *stg, cons
         float yy[4];
         output_transform(m, yy);
         float *dst = ybase + (size_t)round_filter<V>(kl, r) * plane + lane;
-        dst[0] = yy[0];
-        if (col1) dst[dW] = yy[1];
-        if (row1) {
-          dst[dH] = yy[2];
-          if (col1) dst[dH + dW] = yy[3];
+        if (n_ok) {
+          dst[0] = yy[0];
+          if (col1) dst[dW] = yy[1];
+          if (row1) {
+            dst[dH] = yy[2];
+            if (col1) dst[dH + dW] = yy[3];
+          }
         }
       }
     }

@@ -392,7 +392,8 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
             for (int q = 0; q < 4; ++q) yq[h2][q][e] = yy[q];
           }
         }
-        if (valid) {
+        // eight images per lane and step; N is a multiple of 8, so a step is inside N or outside
+        if (valid && tc.nb * kTcN + 4 * (jbase + jj) < p.N) {
           float *dst = ybase + 4 * (jbase + jj);
           st_global_v8(dst, yq[0][0], yq[1][0]);
           if (col1) st_global_v8(dst + dW, yq[0][1], yq[1][1]);

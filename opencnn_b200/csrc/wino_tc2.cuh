@@ -333,7 +333,8 @@ __device__ __forceinline__ void p2_body(const CUtensorMap &tm_in, const CUtensor
 #pragma unroll
               for (int q = 0; q < 4; ++q) yq[q][e] = yy[q];
             }
-            if (kvalid) {
+            // eight images per lane and step; N is a multiple of 8, so a step is inside N or outside
+            if (kvalid && (2 * tc.np + ib) * 32 + 16 * sub + 8 * step < p.N) {
               float *dst = ybase + 8 * step;
 #pragma unroll
               for (int q = 0; q < 4; ++q) {

@@ -59,6 +59,34 @@ def test_matches_oracle_bit_for_bit(oracle, libs, variant, shape):
     assert np.array_equal(y, expect), f"max |diff| {np.abs(y - expect).max()}"
 
 
+# Batches that are not a multiple of 32 (an extension over the reference, which needs N % 32 == 0): the last
+# image block is ragged.  Accepted by the opencnn_* entries for N % 4 == 0; the legacy entries still refuse.
+RAGGED = [(36, 8, 64, 5, 5), (44, 16, 64, 6, 4), (100, 8, 128, 3, 3), (4, 8, 64, 4, 4), (60, 8, 64, 7, 7)]
+
+
+@pytest.mark.parametrize("variant", build.VARIANTS)
+@pytest.mark.parametrize("shape", RAGGED)
+def test_ragged_batch_bit_for_bit(oracle, libs, variant, shape):
+    N, C, K, H, W = shape
+    x, g = oracle.input_chwn(N, C, H, W), oracle.filter_crsk(C, K)
+    dx, dg = torch.from_numpy(x).cuda(), torch.from_numpy(g).cuda()
+    guard = 4096                                    # floats after the output that must stay untouched
+    flat = torch.full((K * H * W * N + guard,), float("nan"), device="cuda")
+    dy = flat[:K * H * W * N].view(K, H, W, N)
+    dws = torch.empty((C, 4, 4, K), device="cuda")
+    assert api.call_like_reference(dx, dg, dy, dws, N, C, H, W, K, variant=variant) != 0 or H != W, \
+        "the legacy entry keeps N % 32 == 0"
+    err = api.conv3x3(dx, dg, dy, dws, N, C, H, W, K, stream=torch.cuda.current_stream().cuda_stream, variant=variant)
+    assert err == 0, f"cudaError {err}"
+    assert api.last_device_status(variant) == 0
+    got = flat.cpu().numpy()
+    assert np.isnan(got[K * H * W * N:]).all(), "wrote past the end of the output"
+    y = got[:K * H * W * N].reshape(K, H, W, N)
+    expect = oracle.forward(x, g)
+    assert np.array_equal(y, expect), f"max |diff| {np.nanmax(np.abs(y - expect))}"
+    assert api.conv3x3(dx, dg, dy, dws, N + 2, C, H, W, K, variant=variant) != 0, "N % 4 != 0 must be refused"
+
+
 @pytest.mark.parametrize("variant", build.VARIANTS)
 def test_integer_known_answers_are_exact(oracle, libs, variant):
     for N, C, K, H, W in [(32, 8, 64, 5, 5), (64, 16, 64, 8, 8)]:

@@ -54,6 +54,29 @@ def test_tensor_core_path(oracle, libs, precision, shape):
     assert tworst <= TRUTH_REL[precision] * trms, f"vs fp64: {tworst / trms:.3e} of rms"
 
 
+# Ragged last image block (N % 8 == 0 on this path), single-CTA kernel and CTA-pair kernel (>= 32 K-steps, N >= 64).
+RAGGED = [(40, 16, 128, 6, 6), (72, 32, 64, 5, 7), (8, 16, 128, 4, 4), (72, 512, 128, 4, 4), (104, 512, 128, 3, 3)]
+
+
+@pytest.mark.parametrize("precision", ["tf32", "bf16"])
+@pytest.mark.parametrize("shape", RAGGED)
+def test_ragged_batch_on_tensor_cores(oracle, libs, precision, shape):
+    N, C, K, H, W = shape
+    rnd = oracle.round_tf32 if precision == "tf32" else oracle.round_bf16
+    x = rnd(oracle.input_chwn(N, C, H, W)).reshape(C, H, W, N)
+    g = rnd(oracle.filter_crsk(C, K)).reshape(C, 3, 3, K)
+    y = run_tc(x, g, precision)
+    assert np.isfinite(y).all()
+    model = oracle.tc_model(x, g, precision)
+    rms = float(np.sqrt(np.mean(model.astype(np.float64) ** 2)))
+    worst = float(np.abs(y - model).max())
+    assert worst <= MODEL_REL * max(rms, 1e-30), f"vs model: {worst / rms:.3e} of rms"
+    dx = torch.zeros((C, H, W, N + 4), device="cuda")
+    assert api.conv3x3(dx, torch.from_numpy(g).cuda(), torch.empty((K, H, W, N + 4), device="cuda"),
+                       torch.empty((C, 4, 4, K), device="cuda"), N + 4, C, H, W, K, precision=precision) != 0, \
+        "N % 8 != 0 must be refused on the tensor-core path"
+
+
 @pytest.mark.parametrize("precision", ["tf32", "bf16"])
 def test_integer_tensors_are_exact_on_tensor_cores(oracle, libs, precision):
     """Small integers are exact in both operand types and in the fp32 accumulator."""
