@@ -74,17 +74,21 @@ cudaError_t device_state(DeviceState **out) {
   std::call_once(st.once, [&] {
     cudaError_t err = cudaDeviceGetAttribute(&st.sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (err == cudaSuccess)
-      err = cudaFuncSetAttribute(ocb::wino_fp32_kernel<OCB_VARIANT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      err = cudaFuncSetAttribute(ocb::wino_fp32_kernel<OCB_VARIANT, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)ocb::SmemLayout<OCB_VARIANT>::kBytes);
+    if (err == cudaSuccess)
+      err = cudaFuncSetAttribute(ocb::wino_fp32_kernel<OCB_VARIANT, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)ocb::SmemLayout<OCB_VARIANT>::kBytes);
     if (err == cudaSuccess) {
       // The kernel redistributes registers with setmaxnreg; that only works if the compiler gave
       // the CTA at least the pool the budgets add up to.  Refuse to run a build where it did not
       // (its consumer warps would wait for registers for ever).
+      constexpr int kBudget = ocb::kConsumerThreads * ocb::kConsumerRegs + ocb::kProducerThreads * ocb::kProducerRegs;
       cudaFuncAttributes fa;
-      err = cudaFuncGetAttributes(&fa, ocb::wino_fp32_kernel<OCB_VARIANT>);
-      if (err == cudaSuccess && fa.numRegs * ocb::kThreads < ocb::kConsumerThreads * ocb::kConsumerRegs +
-                                                                 ocb::kProducerThreads * ocb::kProducerRegs)
-        err = cudaErrorLaunchOutOfResources;
+      err = cudaFuncGetAttributes(&fa, ocb::wino_fp32_kernel<OCB_VARIANT, false>);
+      if (err == cudaSuccess && fa.numRegs * ocb::kThreads < kBudget) err = cudaErrorLaunchOutOfResources;
+      if (err == cudaSuccess) err = cudaFuncGetAttributes(&fa, ocb::wino_fp32_kernel<OCB_VARIANT, true>);
+      if (err == cudaSuccess && fa.numRegs * ocb::kThreads < kBudget) err = cudaErrorLaunchOutOfResources;
     }
     if (err == cudaSuccess)
       err = cudaFuncSetAttribute(ocb::wino_tc_kernel<ocb::kTcBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -124,17 +128,20 @@ cudaError_t device_state(DeviceState **out) {
 
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
-// `n_multiple`: what the batch must be a multiple of.  The two legacy entry points keep the
-// reference's rule (32).  The other entries accept a ragged last block of images: 4 on the fp32
-// path (rows of the tensors must stay 16-byte aligned for TMA), 8 on the tensor-core path (its
-// epilogue stores eight images per lane).  Loads of the missing images are zero-filled by TMA,
-// their outputs are not stored.
-constexpr int kLegacyBatchMultiple = 32;
-int batch_multiple(int precision) { return precision == OPENCNN_FP32 ? 4 : 8; }
+// What the batch and the channel count must be multiples of.  The two legacy entry points keep
+// the reference's rules (N % 32, C % 8).  The other entries accept a ragged last block of images
+// - N % 4 on the fp32 path (rows of the tensors must stay 16-byte aligned for TMA), N % 8 on the
+// tensor-core path (its epilogue stores eight images per lane) - and any channel count: images
+// and channels beyond the end are zero-filled by TMA, which leaves every fma chain unchanged
+// (fma(0, 0, acc) == acc for the accumulators that occur, which are never -0), and outputs of
+// missing images are not stored.
+struct ShapeRule { int n_multiple, c_multiple; };
+constexpr ShapeRule kLegacyRule = {32, 8};
+ShapeRule shape_rule(int precision) { return ShapeRule{precision == OPENCNN_FP32 ? 4 : 8, 1}; }
 
-cudaError_t check_shape(int N, int C, int H, int W, int K, int n_multiple) {
+cudaError_t check_shape(int N, int C, int H, int W, int K, ShapeRule rule) {
   if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || K <= 0) return cudaErrorInvalidValue;
-  if (N % n_multiple || K % ocb::kBK || C % ocb::kBC) return cudaErrorInvalidValue;
+  if (N % rule.n_multiple || K % ocb::kBK || C % rule.c_multiple) return cudaErrorInvalidValue;
   // 32-bit tile arithmetic and TMA extents
   if ((long long)N * C * H * W >= (1ll << 40) || (long long)N * K * H * W >= (1ll << 40)) return cudaErrorInvalidValue;
   return cudaSuccess;
@@ -188,7 +195,7 @@ cudaError_t launch_wino_fp32(const float *input, const float *workspace, float *
   const long long tiles = (long long)p.tiles_h * p.tiles_w * p.n_blocks * p.k_blocks;
   if (tiles > 0x7fffffffll / 8) return cudaErrorInvalidValue;
   p.total_tiles = (int)tiles;
-  p.chunks_per_tile = C / ocb::kBC;
+  p.chunks_per_tile = (C + ocb::kBC - 1) / ocb::kBC;
   p.status = st->status_ptr;
   const int grid = p.total_tiles < st->sm_count ? p.total_tiles : st->sm_count;
   // The last round of the persistent schedule is usually only partly filled.  If its tiles, cut in
@@ -201,7 +208,10 @@ cudaError_t launch_wino_fp32(const float *input, const float *workspace, float *
     p.split_from = full_rounds * grid;
     p.total_items = p.split_from + 2 * rest;
   }
-  ocb::wino_fp32_kernel<OCB_VARIANT><<<grid, ocb::kThreads, ocb::SmemLayout<OCB_VARIANT>::kBytes, stream>>>(tm_in, tm_u, p);
+  if (N % ocb::kBN == 0)
+    ocb::wino_fp32_kernel<OCB_VARIANT, false><<<grid, ocb::kThreads, ocb::SmemLayout<OCB_VARIANT>::kBytes, stream>>>(tm_in, tm_u, p);
+  else   // ragged last image block: stores masked per image
+    ocb::wino_fp32_kernel<OCB_VARIANT, true><<<grid, ocb::kThreads, ocb::SmemLayout<OCB_VARIANT>::kBytes, stream>>>(tm_in, tm_u, p);
   return cudaGetLastError();
 }
 
@@ -343,11 +353,11 @@ cudaError_t launch_tc(const float *input, const float *workspace, float *output,
 }
 
 cudaError_t forward(const float *input, const float *filter, float *output, float *workspace, int N, int C, int H,
-                    int W, int K, int precision, cudaStream_t stream, int n_multiple) {
+                    int W, int K, int precision, cudaStream_t stream, ShapeRule rule) {
   if (!input || !filter || !output || !workspace) return cudaErrorInvalidValue;
   if (!aligned16(input) || !aligned16(filter) || !aligned16(output) || !aligned16(workspace)) return cudaErrorInvalidValue;
   if (precision != OPENCNN_FP32 && precision != OPENCNN_TF32 && precision != OPENCNN_BF16) return cudaErrorInvalidValue;
-  cudaError_t e = check_shape(N, C, H, W, K, n_multiple);
+  cudaError_t e = check_shape(N, C, H, W, K, rule);
   if (e != cudaSuccess) return e;
   if (precision == OPENCNN_BF16) {
     e = launch_fx_tc<ocb::kTcBf16>(filter, workspace, C, K, stream);
@@ -412,7 +422,7 @@ int convolutionForward_32x64x8(float *k, int in_h, int in_w, float *w, int out_h
   if (filt_c != in_c || out_c != filt_k || out_n != in_n || out_h != in_h || out_w != in_w)
     return (int)cudaErrorInvalidValue;
   if (tiles_dim != (in_w + 1) / 2) return (int)cudaErrorInvalidValue;
-  return (int)forward(k, w, C, Ww, in_n, in_c, in_h, in_w, filt_k, OPENCNN_FP32, (cudaStream_t)0, kLegacyBatchMultiple);
+  return (int)forward(k, w, C, Ww, in_n, in_c, in_h, in_w, filt_k, OPENCNN_FP32, (cudaStream_t)0, kLegacyRule);
 }
 
 int convolutionForward(float *k, int in_h, int in_w, float *w, int out_h, int out_w, int out_n, int out_c,
@@ -428,7 +438,7 @@ int opencnn_convolutionForward_stream(const float *input, const float *filter, f
                                       int in_n, int in_c, int in_h, int in_w, int filt_k, int precision,
                                       opencnn_stream_t stream) {
   return (int)forward(input, filter, output, workspace, in_n, in_c, in_h, in_w, filt_k, precision,
-                      (cudaStream_t)stream, batch_multiple(precision));
+                      (cudaStream_t)stream, shape_rule(precision));
 }
 
 int opencnn_filter_transform(const float *filter, float *workspace, int in_c, int filt_k, opencnn_stream_t stream) {
@@ -450,7 +460,7 @@ int opencnn_winograd_forward(const float *input, const float *workspace, float *
   if (!input || !workspace || !output) return (int)cudaErrorInvalidValue;
   if (!aligned16(input) || !aligned16(workspace) || !aligned16(output)) return (int)cudaErrorInvalidValue;
   if (precision != OPENCNN_FP32 && precision != OPENCNN_TF32 && precision != OPENCNN_BF16) return (int)cudaErrorInvalidValue;
-  cudaError_t e = check_shape(in_n, in_c, in_h, in_w, filt_k, batch_multiple(precision));
+  cudaError_t e = check_shape(in_n, in_c, in_h, in_w, filt_k, shape_rule(precision));
   if (e != cudaSuccess) return (int)e;
   if (precision == OPENCNN_BF16)
     return (int)launch_tc<ocb::kTcBf16>(input, workspace, output, in_n, in_c, in_h, in_w, filt_k, (cudaStream_t)stream);
@@ -464,7 +474,7 @@ int opencnn_convolutionForward_noalloc(const float *input, const float *filter, 
                                        int in_c, int in_h, int in_w, int filt_k, opencnn_stream_t stream) {
   if (!input || !filter || !output) return (int)cudaErrorInvalidValue;
   if (!aligned16(input) || !aligned16(filter) || !aligned16(output)) return (int)cudaErrorInvalidValue;
-  cudaError_t e = check_shape(in_n, in_c, in_h, in_w, filt_k, batch_multiple(OPENCNN_FP32));
+  cudaError_t e = check_shape(in_n, in_c, in_h, in_w, filt_k, shape_rule(OPENCNN_FP32));
   if (e != cudaSuccess) return (int)e;
   if ((long long)in_c * filt_k > (long long)OPENCNN_NOALLOC_MAX_CK) {
     std::fprintf(stderr,
@@ -516,7 +526,7 @@ int opencnn_host_plan_create(void **plan, int in_n, int in_c, int in_h, int in_w
   if (!plan) return (int)cudaErrorInvalidValue;
   *plan = nullptr;
   if (precision != OPENCNN_FP32 && precision != OPENCNN_TF32 && precision != OPENCNN_BF16) return (int)cudaErrorInvalidValue;
-  cudaError_t e = check_shape(in_n, in_c, in_h, in_w, filt_k, batch_multiple(precision));
+  cudaError_t e = check_shape(in_n, in_c, in_h, in_w, filt_k, shape_rule(precision));
   if (e != cudaSuccess) return (int)e;
   HostPlan *hp = new (std::nothrow) HostPlan;
   if (!hp) return (int)cudaErrorMemoryAllocation;
@@ -546,7 +556,7 @@ int opencnn_host_plan_run_async(void *plan, const float *input_host, const float
   if (e == cudaSuccess) e = cudaMemcpyAsync(hp->d_in, input_host, in_b, cudaMemcpyHostToDevice, hp->stream);
   if (e == cudaSuccess)
     e = forward(hp->d_in, hp->d_filt, hp->d_out, hp->d_ws, hp->N, hp->C, hp->H, hp->W, hp->K, hp->precision, hp->stream,
-                batch_multiple(hp->precision));
+                shape_rule(hp->precision));
   if (e == cudaSuccess) e = cudaMemcpyAsync(output_host, hp->d_out, out_b, cudaMemcpyDeviceToHost, hp->stream);
   return (int)e;
 }

@@ -185,7 +185,7 @@ __device__ __forceinline__ void group_barrier(int gi) {
 //   OPTLDS64      deposit as OPTSTS64, read back 16 x LDS.64, float2 stores
 // Only the group's own named barrier is used, so the other group keeps computing meanwhile.
 // ---------------------------------------------------------------------------------------------
-template <int V>
+template <int V, bool RAGGED>
 __device__ __forceinline__ void epilogue(uint64_t (&acc)[8][8], float *stg, const WinoParams &p,
                                          const TileCoord &tc, const LaneRole &role) {
   const int lane = threadIdx.x & 31;
@@ -197,10 +197,10 @@ __device__ __forceinline__ void epilogue(uint64_t (&acc)[8][8], float *stg, cons
   float *ybase = p.y + ((size_t)oh0 * p.W + ow0) * p.N + (size_t)tc.nb * kBN +
                  ((size_t)tc.kb * kBK + 32 * role.gi) * plane;
   const size_t dW = (size_t)p.N, dH = (size_t)p.W * p.N;
-  // Ragged last image block (N not a multiple of 32): the missing images were loaded as zeros and
-  // are not stored.  N is a multiple of 4, so an image pair is either inside or outside.
-  const int n_left = p.N - tc.nb * kBN;
-  const bool n_ok = (V == kOptLds64 ? 2 * (lane & 15) : lane) < n_left;
+  // Ragged last image block (N not a multiple of 32; its own kernel instantiation, so that the
+  // usual case pays nothing): the missing images were loaded as zeros and are not stored.  N is a
+  // multiple of 4, so an image pair is either inside or outside.
+  const bool n_ok = !RAGGED || (V == kOptLds64 ? 2 * (lane & 15) : lane) < p.N - tc.nb * kBN;
 
 #pragma unroll
   for (int r = 0; r < 4; ++r) {
@@ -375,7 +375,7 @@ __device__ __forceinline__ void fma_frag(uint64_t (&acc)[8][8], const Frag &f) {
 #endif
 }
 
-template <int V>
+template <int V, bool RAGGED>
 __global__ void __launch_bounds__(kThreads, 1)
 wino_fp32_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ CUtensorMap tm_u,
                  const WinoParams p) {
@@ -512,7 +512,7 @@ wino_fp32_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constan
       }
       const TileCoord tc = decode_tile(p, tile);
       if (!(OCB_ABLATE & 4)) {
-        epilogue<V>(acc, my_stg, p, tc, role);
+        epilogue<V, RAGGED>(acc, my_stg, p, tc, role);
       } else {                                                    // keeps the accumulators alive
         uint64_t x = 0;
 #pragma unroll

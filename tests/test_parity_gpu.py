@@ -87,6 +87,30 @@ def test_ragged_batch_bit_for_bit(oracle, libs, variant, shape):
     assert api.conv3x3(dx, dg, dy, dws, N + 2, C, H, W, K, variant=variant) != 0, "N % 4 != 0 must be refused"
 
 
+# Channel counts that are not a multiple of 8 (another extension; e.g. the 3 channels of a first layer).
+ODD_CHANNELS = [(32, 3, 64, 8, 8), (32, 1, 64, 5, 5), (64, 12, 64, 7, 7), (36, 19, 128, 4, 6)]
+
+
+@pytest.mark.parametrize("variant", build.VARIANTS)
+@pytest.mark.parametrize("shape", ODD_CHANNELS)
+def test_any_channel_count_bit_for_bit(oracle, libs, variant, shape):
+    N, C, K, H, W = shape
+    x, g = oracle.input_chwn(N, C, H, W), oracle.filter_crsk(C, K)
+    dx, dg = torch.from_numpy(x).cuda(), torch.from_numpy(g).cuda()
+    dy = torch.full((K, H, W, N), float("nan"), device="cuda")
+    dws = torch.full((C, 4, 4, K), float("nan"), device="cuda")
+    if H == W and N % 32 == 0:
+        assert api.call_like_reference(dx, dg, dy, dws, N, C, H, W, K, variant=variant) != 0, \
+            "the legacy entry keeps C % 8 == 0"
+    err = api.conv3x3(dx, dg, dy, dws, N, C, H, W, K, stream=torch.cuda.current_stream().cuda_stream, variant=variant)
+    assert err == 0, f"cudaError {err}"
+    assert api.last_device_status(variant) == 0
+    assert np.array_equal(dws.cpu().numpy(), oracle.filter_transform(g)), "filter transform"
+    y, expect = dy.cpu().numpy(), oracle.forward(x, g)
+    assert within(y, oracle.direct_f64(x, g)), "fp64 ground truth, 1e-4 relative"
+    assert np.array_equal(y, expect), f"max |diff| {np.nanmax(np.abs(y - expect))}"
+
+
 @pytest.mark.parametrize("variant", build.VARIANTS)
 def test_integer_known_answers_are_exact(oracle, libs, variant):
     for N, C, K, H, W in [(32, 8, 64, 5, 5), (64, 16, 64, 8, 8)]:

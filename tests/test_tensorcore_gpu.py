@@ -55,7 +55,8 @@ def test_tensor_core_path(oracle, libs, precision, shape):
 
 
 # Ragged last image block (N % 8 == 0 on this path), single-CTA kernel and CTA-pair kernel (>= 32 K-steps, N >= 64).
-RAGGED = [(40, 16, 128, 6, 6), (72, 32, 64, 5, 7), (8, 16, 128, 4, 4), (72, 512, 128, 4, 4), (104, 512, 128, 3, 3)]
+RAGGED = [(40, 16, 128, 6, 6), (72, 32, 64, 5, 7), (8, 16, 128, 4, 4), (72, 512, 128, 4, 4), (104, 512, 128, 3, 3),
+          (32, 3, 64, 6, 6), (40, 21, 128, 5, 5), (64, 515, 128, 3, 3)]   # and channel counts that are not a multiple of 8
 
 
 @pytest.mark.parametrize("precision", ["tf32", "bf16"])
