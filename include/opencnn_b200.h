@@ -11,7 +11,8 @@
  * the reference, violations are reported (cudaErrorInvalidValue) instead of computing garbage,
  * and rectangular images (in_h != in_w) are accepted.  The two legacy entry points keep
  * N % 32 == 0 and C % 8 == 0; every opencnn_* entry also takes a ragged last block of images
- * (N % 4 == 0 with OPENCNN_FP32, N % 8 == 0 with OPENCNN_TF32 / OPENCNN_BF16) and any in_c >= 1.
+ * (N % 4 == 0 with OPENCNN_FP32, N % 8 == 0 with OPENCNN_TF32 / OPENCNN_BF16), any in_c >= 1 and,
+ * with OPENCNN_FP32, filt_k % 4 == 0.
  *
  * Return values are cudaError_t codes passed as int, so the header needs no CUDA include.
  * All pointers are device pointers unless a function says otherwise.  Calls are asynchronous

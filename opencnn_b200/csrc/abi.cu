@@ -131,17 +131,21 @@ bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 // What the batch and the channel count must be multiples of.  The two legacy entry points keep
 // the reference's rules (N % 32, C % 8).  The other entries accept a ragged last block of images
 // - N % 4 on the fp32 path (rows of the tensors must stay 16-byte aligned for TMA), N % 8 on the
-// tensor-core path (its epilogue stores eight images per lane) - and any channel count: images
-// and channels beyond the end are zero-filled by TMA, which leaves every fma chain unchanged
+// tensor-core path (its epilogue stores eight images per lane) - and any channel count; on the
+// fp32 path also a ragged last block of filters (K % 4; the tensor-core path views the
+// transformed filter in rows of 64 filters and keeps K % 64).  Images, channels and filters
+// beyond the end are zero-filled by TMA, which leaves every fma chain unchanged
 // (fma(0, 0, acc) == acc for the accumulators that occur, which are never -0), and outputs of
-// missing images are not stored.
-struct ShapeRule { int n_multiple, c_multiple; };
-constexpr ShapeRule kLegacyRule = {32, 8};
-ShapeRule shape_rule(int precision) { return ShapeRule{precision == OPENCNN_FP32 ? 4 : 8, 1}; }
+// missing images and filters are not stored.
+struct ShapeRule { int n_multiple, c_multiple, k_multiple; };
+constexpr ShapeRule kLegacyRule = {32, 8, 64};
+ShapeRule shape_rule(int precision) {
+  return precision == OPENCNN_FP32 ? ShapeRule{4, 1, 4} : ShapeRule{8, 1, 64};
+}
 
 cudaError_t check_shape(int N, int C, int H, int W, int K, ShapeRule rule) {
   if (N <= 0 || C <= 0 || H <= 0 || W <= 0 || K <= 0) return cudaErrorInvalidValue;
-  if (N % rule.n_multiple || K % ocb::kBK || C % rule.c_multiple) return cudaErrorInvalidValue;
+  if (N % rule.n_multiple || K % rule.k_multiple || C % rule.c_multiple) return cudaErrorInvalidValue;
   // 32-bit tile arithmetic and TMA extents
   if ((long long)N * C * H * W >= (1ll << 40) || (long long)N * K * H * W >= (1ll << 40)) return cudaErrorInvalidValue;
   return cudaSuccess;
@@ -191,7 +195,7 @@ cudaError_t launch_wino_fp32(const float *input, const float *workspace, float *
   p.tiles_h = (H + 1) / 2;
   p.tiles_w = (W + 1) / 2;
   p.n_blocks = (N + ocb::kBN - 1) / ocb::kBN;
-  p.k_blocks = K / ocb::kBK;
+  p.k_blocks = (K + ocb::kBK - 1) / ocb::kBK;
   const long long tiles = (long long)p.tiles_h * p.tiles_w * p.n_blocks * p.k_blocks;
   if (tiles > 0x7fffffffll / 8) return cudaErrorInvalidValue;
   p.total_tiles = (int)tiles;
@@ -208,9 +212,9 @@ cudaError_t launch_wino_fp32(const float *input, const float *workspace, float *
     p.split_from = full_rounds * grid;
     p.total_items = p.split_from + 2 * rest;
   }
-  if (N % ocb::kBN == 0)
+  if (N % ocb::kBN == 0 && K % ocb::kBK == 0)
     ocb::wino_fp32_kernel<OCB_VARIANT, false><<<grid, ocb::kThreads, ocb::SmemLayout<OCB_VARIANT>::kBytes, stream>>>(tm_in, tm_u, p);
-  else   // ragged last image block: stores masked per image
+  else   // ragged last block of images or filters: stores masked
     ocb::wino_fp32_kernel<OCB_VARIANT, true><<<grid, ocb::kThreads, ocb::SmemLayout<OCB_VARIANT>::kBytes, stream>>>(tm_in, tm_u, p);
   return cudaGetLastError();
 }

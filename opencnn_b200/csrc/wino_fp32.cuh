@@ -197,10 +197,11 @@ __device__ __forceinline__ void epilogue(uint64_t (&acc)[8][8], float *stg, cons
   float *ybase = p.y + ((size_t)oh0 * p.W + ow0) * p.N + (size_t)tc.nb * kBN +
                  ((size_t)tc.kb * kBK + 32 * role.gi) * plane;
   const size_t dW = (size_t)p.N, dH = (size_t)p.W * p.N;
-  // Ragged last image block (N not a multiple of 32; its own kernel instantiation, so that the
-  // usual case pays nothing): the missing images were loaded as zeros and are not stored.  N is a
-  // multiple of 4, so an image pair is either inside or outside.
+  // Ragged last block of images or filters (N not a multiple of 32, K not of 64; its own kernel
+  // instantiation, so that the usual case pays nothing): what is missing was loaded as zeros and
+  // is not stored.  N is a multiple of 4, so an image pair is either inside or outside.
   const bool n_ok = !RAGGED || (V == kOptLds64 ? 2 * (lane & 15) : lane) < p.N - tc.nb * kBN;
+  const int k_left = p.K - (tc.kb * kBK + 32 * role.gi);              // filters of this group's 32 that exist
 
 #pragma unroll
   for (int r = 0; r < 4; ++r) {
@@ -240,7 +241,7 @@ __device__ __forceinline__ void epilogue(uint64_t (&acc)[8][8], float *stg, cons
       output_transform(m0, y0);
       output_transform(m1, y1);
       float *dst = ybase + (size_t)round_filter<V>(kl, r) * plane + 2 * np;
-      if (n_ok) {
+      if (n_ok && (!RAGGED || round_filter<V>(kl, r) < k_left)) {
         *reinterpret_cast<float2 *>(dst) = make_float2(y0[0], y1[0]);
         if (col1) *reinterpret_cast<float2 *>(dst + dW) = make_float2(y0[1], y1[1]);
         if (row1) {
@@ -262,7 +263,7 @@ __device__ __forceinline__ void epilogue(uint64_t (&acc)[8][8], float *stg, cons
         float yy[4];
         output_transform(m, yy);
         float *dst = ybase + (size_t)round_filter<V>(kl, r) * plane + lane;
-        if (n_ok) {
+        if (n_ok && (!RAGGED || round_filter<V>(kl, r) < k_left)) {
           dst[0] = yy[0];
           if (col1) dst[dW] = yy[1];
           if (row1) {

@@ -87,8 +87,10 @@ def test_ragged_batch_bit_for_bit(oracle, libs, variant, shape):
     assert api.conv3x3(dx, dg, dy, dws, N + 2, C, H, W, K, variant=variant) != 0, "N % 4 != 0 must be refused"
 
 
-# Channel counts that are not a multiple of 8 (another extension; e.g. the 3 channels of a first layer).
-ODD_CHANNELS = [(32, 3, 64, 8, 8), (32, 1, 64, 5, 5), (64, 12, 64, 7, 7), (36, 19, 128, 4, 6)]
+# Channel counts that are not a multiple of 8 (e.g. the 3 channels of a first layer) and filter counts that are
+# not a multiple of 64 (fp32 path: K % 4 == 0): further extensions over the reference.
+ODD_CHANNELS = [(32, 3, 64, 8, 8), (32, 1, 64, 5, 5), (64, 12, 64, 7, 7), (36, 19, 128, 4, 6),
+                (32, 8, 96, 6, 6), (32, 16, 4, 5, 5), (64, 8, 132, 3, 3), (44, 5, 68, 4, 4)]
 
 
 @pytest.mark.parametrize("variant", build.VARIANTS)
@@ -109,6 +111,9 @@ def test_any_channel_count_bit_for_bit(oracle, libs, variant, shape):
     y, expect = dy.cpu().numpy(), oracle.forward(x, g)
     assert within(y, oracle.direct_f64(x, g)), "fp64 ground truth, 1e-4 relative"
     assert np.array_equal(y, expect), f"max |diff| {np.nanmax(np.abs(y - expect))}"
+    if K % 64:
+        assert api.conv3x3(dx, dg, dy, dws, N, C, H, W, K, precision="tf32", variant=variant) != 0 or N % 8, \
+            "the tensor-core path keeps K % 64 == 0"
 
 
 @pytest.mark.parametrize("variant", build.VARIANTS)
