@@ -109,7 +109,7 @@ int opencnn_last_device_status(void);
  *    problems are refused with cudaErrorInvalidValue and a message on stderr.  Use the entry
  *    points above with your own workspace for those.
  *  - The first call on each device looks up the array's device address (and does the library's
- *    usual one-time kernel set-up), so make that first call outside any stream capture.
+ *    usual one-time kernel set-up); later calls on that device do neither.
  *  - All calls on a device share the one array.  Nothing in it has to start at zero - every call
  *    first overwrites the part it then reads - but it does keep the previous call's contents, and
  *    two calls whose kernels overlap on the GPU (different streams, no ordering) race on it.
