@@ -208,6 +208,11 @@ __device__ __forceinline__ void transform_to_v_tf32(const float *raw, uint8_t *v
   }
 }
 
+// True when the tile's accumulator rows 64-127 repeat rows 0-63 (see the MMA issuer).
+template <int DT> __device__ __forceinline__ bool tile_repeats_filters(const WinoParams &p, const TileCoord &tc) {
+  return DT == kTcBf16 && p.K - tc.kb * kTcM <= 64;
+}
+
 // p.k_blocks counts 128-filter blocks here.
 template <int DT>
 __global__ void __launch_bounds__(kTcThreads, 1)
@@ -326,6 +331,11 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
       // B: 32 images x KC channels, image-contiguous rows (64 B bf16 / 128 B tf32), 8-channel groups 512 B apart.
       // TF32 (32-bit, MN-major) uses the 128B-swizzle-with-32B-atom mode: 4-channel groups 512 B apart.
       const uint64_t a_desc0 = DT == kTcBf16 ? smem_desc(smem_u32(u_s), KC * 128, 1024, 2) : smem_desc(smem_u32(u_s), KC * 128, 512, 1);
+      // When at most 64 of the tile's 128 filters exist (K = 64 layers) the second 64-filter block of the BF16
+      // A operand is made to alias the first (block stride 0): accumulator rows 64-127 then repeat rows 0-63,
+      // and the epilogue warps that own those TMEM lanes take half of the images instead of idling.
+      const uint64_t a_desc0_dup = smem_desc(smem_u32(u_s), 0, 1024, 2);
+      bool dup = tile_repeats_filters<DT>(p, decode_tile(p, (int)blockIdx.x));
       const uint64_t b_desc0 = DT == kTcBf16 ? smem_desc(smem_u32(v_s), 512, 512, 4) : smem_desc(smem_u32(v_s), 1024, 512, 1);
       int ci = 0, seq = 0;
       for (int g = 0; g < total_chunks; ++g) {
@@ -335,7 +345,7 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
         mbar_wait(smem_u32(v_ready + s), use & 1, dead, p.status);
         if (ci == 0 && seq > 0) mbar_wait(smem_u32(acc_empty), (seq - 1) & 1, dead, p.status);   // TMEM drained
         tc_fence_after();
-        const uint64_t ad = a_desc0 + (uint64_t)(s * (kTcUBytes >> 4)), bd = b_desc0 + (uint64_t)(s * (kTcVBytes >> 4));
+        const uint64_t ad = (dup ? a_desc0_dup : a_desc0) + (uint64_t)(s * (kTcUBytes >> 4)), bd = b_desc0 + (uint64_t)(s * (kTcVBytes >> 4));
         const uint32_t accumulate = ci > 0 ? 1u : 0u;
 #pragma unroll
         for (int xi = 0; xi < ((OCB_TC_ABLATE & 8) ? 0 : 16); ++xi)
@@ -345,19 +355,26 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
           tc_commit(smem_u32(acc_full));                   // tile finished
           ci = 0;
           ++seq;
+          if (seq < my_tiles) dup = tile_repeats_filters<DT>(p, decode_tile(p, (int)blockIdx.x + seq * (int)gridDim.x));
         }
       }
     }
   } else {
     // ===================================== epilogue ============================================
     const int quarter = warp & 3;                                        // TMEM lanes this warp may read
-    const int m = quarter * 32 + lane;                                   // filter within the tile
+    const int sub = (warp - 6) >> 2;                                     // 0 / 1: the two warps of a lane quarter
     const size_t plane = (size_t)p.H * p.W * p.N;
     const size_t dW = (size_t)p.N, dH = (size_t)p.W * p.N;
     for (int seq = 0; seq < my_tiles; ++seq) {
       const TileCoord tc = decode_tile(p, (int)blockIdx.x + seq * (int)gridDim.x);
       mbar_wait(smem_u32(acc_full), seq & 1, dead, p.status);
       tc_fence_after();
+      // Usually the quarter's lanes are filters 32*quarter .. +31 and the two warps of a quarter split the 32
+      // images 16 / 16 (two steps of 8).  With repeated filters, quarters 2 and 3 hold filters 0-63 again, so
+      // the eight warps split the images 8 each (one step).
+      const bool dup = tile_repeats_filters<DT>(p, tc);
+      const int fq = dup ? (quarter & 1) : quarter;                      // filter block of 32 this warp stores
+      const int m = fq * 32 + lane;                                      // filter within the tile
       const int k = tc.kb * kTcM + m;
       const bool valid = k < p.K;
       const int oh0 = 2 * tc.ty, ow0 = 2 * tc.tx;
@@ -365,12 +382,12 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
       float *ybase = p.y + (size_t)k * plane + ((size_t)oh0 * p.W + ow0) * p.N + (size_t)tc.nb * kTcN;
       const uint32_t tlane = tmem_base + ((uint32_t)(quarter * 32) << 16);
       // Warps whose 32 filters all lie beyond K (K = 64 layers) have nothing to read or store.
-      const bool warp_valid = (tc.kb * kTcM + quarter * 32) < p.K;
-      // this warp's share of the 32 images: image quads jbase .. jbase + kIters - 1
-      constexpr int kIters = (OCB_TC_ABLATE & 16) ? 0 : (kTcN / 4) / (kTcEpilogueWarps / 4);
-      const int jbase = ((warp - 6) >> 2) * ((kTcN / 4) / (kTcEpilogueWarps / 4));
+      const bool warp_valid = (tc.kb * kTcM + fq * 32) < p.K;
+      // this warp's share of the 32 images: image quads jbase .. jbase + iters - 1
+      const int iters = (OCB_TC_ABLATE & 16) ? 0 : (dup ? 2 : 4);
+      const int jbase = dup ? 2 * (2 * (quarter >> 1) + sub) : 4 * sub;
 #pragma unroll 1
-      for (int jj = 0; jj < kIters; jj += 2) {
+      for (int jj = 0; jj < iters; jj += 2) {
         if (!warp_valid) break;
         // Two image quads per step so that every store is one full 32-byte sector per lane: lanes
         // are filters, i.e. different output rows, and 16-byte stores would touch twice the sectors.
