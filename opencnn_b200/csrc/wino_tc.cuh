@@ -41,7 +41,9 @@ namespace ocb {
 enum TcType : int { kTcBf16 = 0, kTcTf32 = 1 };
 
 constexpr int kTcEpilogueWarps = 8;
-constexpr int kTcThreads = (6 + kTcEpilogueWarps + 1) * 32;   // + the U loader, last warp
+constexpr int kTcULoaderWarp = 6 + kTcEpilogueWarps;          // warp 14
+constexpr int kTcMmaWarpB = kTcULoaderWarp + 1;               // warp 15: issues the MMAs of positions 8-15
+constexpr int kTcThreads = (kTcMmaWarpB + 1) * 32;
 constexpr int kTcM = 128;                   // filters per CTA tile
 constexpr int kTcN = 32;                    // images per CTA tile
 constexpr int kTcStages = 2;
@@ -51,7 +53,10 @@ constexpr uint32_t kTcVBytes = 16 * 1024;   // 16 positions x (32 images x one K
 template <int DT> struct TcCfg {
   static constexpr int kKC = DT == kTcBf16 ? 16 : 8;                 // channels per K-step / stage
   static constexpr uint32_t kRawBytes = kKC * 16 * kTcN * 4;         // [c][h][w][n] fp32
-  static constexpr size_t kSmemBytes = (size_t)kTcStages * (kRawBytes + kTcUBytes + kTcVBytes) + 1024;
+  // The raw patches have their own ring, as deep as shared memory allows next to two stages of U
+  // and V: TF32 stages are 16 KB (four fit), BF16 stages 32 KB (two).
+  static constexpr int kRawStages = DT == kTcBf16 ? 2 : 4;
+  static constexpr size_t kSmemBytes = (size_t)kRawStages * kRawBytes + (size_t)kTcStages * (kTcUBytes + kTcVBytes) + 1024;
 };
 
 // ---- tcgen05 wrappers ------------------------------------------------------------------------
@@ -221,13 +226,14 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
   constexpr int KC = Cfg::kKC;
   extern __shared__ __align__(1024) uint8_t tsmem[];
   uint8_t *raw_s = tsmem;                                              // [stage][KC][16][32] fp32
-  uint8_t *u_s = raw_s + kTcStages * Cfg::kRawBytes;                   // [stage][16 xi][...]  4 KB per position
+  constexpr int SR = Cfg::kRawStages;
+  uint8_t *u_s = raw_s + SR * Cfg::kRawBytes;                          // [stage][16 xi][...]  4 KB per position
   uint8_t *v_s = u_s + kTcStages * kTcUBytes;                          // [stage][16 xi][...]  1 KB per position
   uint64_t *bars = reinterpret_cast<uint64_t *>(v_s + kTcStages * kTcVBytes);
-  uint64_t *raw_full = bars, *raw_empty = bars + 2, *u_full = bars + 4, *v_ready = bars + 6, *uv_empty = bars + 8;
-  uint64_t *acc_full = bars + 10, *acc_empty = bars + 11;
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + 12);
-  volatile int *dead = reinterpret_cast<volatile int *>(bars + 13);
+  uint64_t *raw_full = bars, *raw_empty = bars + SR, *u_full = bars + 2 * SR, *v_ready = u_full + 2, *uv_empty = u_full + 4;
+  uint64_t *acc_full = u_full + 6, *acc_empty = u_full + 7;
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(u_full + 8);
+  volatile int *dead = reinterpret_cast<volatile int *>(u_full + 9);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int my_tiles = (p.total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
@@ -236,14 +242,16 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
 
   if (tid == 0) {
     *dead = 0;
-    for (int s = 0; s < kTcStages; ++s) {
+    for (int s = 0; s < SR; ++s) {
       mbar_init(smem_u32(raw_full + s), 1);
       mbar_init(smem_u32(raw_empty + s), 4);
+    }
+    for (int s = 0; s < kTcStages; ++s) {
       mbar_init(smem_u32(u_full + s), 1);
       mbar_init(smem_u32(v_ready + s), 4);
-      mbar_init(smem_u32(uv_empty + s), 1);
+      mbar_init(smem_u32(uv_empty + s), 2);      // one tcgen05.commit per MMA-issuing thread
     }
-    mbar_init(smem_u32(acc_full), 1);
+    mbar_init(smem_u32(acc_full), 2);
     mbar_init(smem_u32(acc_empty), kTcEpilogueWarps);
     mbar_fence_init();
   }
@@ -253,7 +261,7 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0 || warp == kTcThreads / 32 - 1) {
+  if (warp == 0 || warp == kTcULoaderWarp) {
     // ===================================== TMA producers =======================================
     // Two independent loaders, so that the input patches (needed early, by the transform) never
     // wait behind the filter slices (whose stage is released late, by the MMAs): warp 0 loads the
@@ -267,12 +275,14 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
         const int s = g % kTcStages;
         const uint32_t use = g / kTcStages;
         if (!loads_u) {
-          if (use > 0) mbar_wait(smem_u32(raw_empty + s), (use - 1) & 1, dead, p.status);
+          const int sr = g % SR;
+          const uint32_t use_r = g / SR;
+          if (use_r > 0) mbar_wait(smem_u32(raw_empty + sr), (use_r - 1) & 1, dead, p.status);
           if (OCB_TC_ABLATE & 2) {
-            mbar_arrive(smem_u32(raw_full + s));
+            mbar_arrive(smem_u32(raw_full + sr));
           } else {
-            mbar_arrive_expect_tx(smem_u32(raw_full + s), Cfg::kRawBytes);
-            tma_load_4d(smem_u32(raw_s + s * Cfg::kRawBytes), &tm_in, smem_u32(raw_full + s), tc.nb * kTcN,
+            mbar_arrive_expect_tx(smem_u32(raw_full + sr), Cfg::kRawBytes);
+            tma_load_4d(smem_u32(raw_s + sr * Cfg::kRawBytes), &tm_in, smem_u32(raw_full + sr), tc.nb * kTcN,
                         2 * tc.tx - 1, 2 * tc.ty - 1, ci * KC);
           }
         } else {
@@ -297,11 +307,11 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
     // ===================================== input transform =====================================
     const int t = tid - 32;                                            // 0..127
     for (int g = 0; g < total_chunks; ++g) {
-      const int s = g % kTcStages;
+      const int s = g % kTcStages, sr = g % SR;
       const uint32_t use = g / kTcStages;
-      mbar_wait(smem_u32(raw_full + s), use & 1, dead, p.status);
+      mbar_wait(smem_u32(raw_full + sr), (g / SR) & 1, dead, p.status);
       if (use > 0) mbar_wait(smem_u32(uv_empty + s), (use - 1) & 1, dead, p.status);   // V stage free again
-      const float *raw = reinterpret_cast<const float *>(raw_s + s * Cfg::kRawBytes);
+      const float *raw = reinterpret_cast<const float *>(raw_s + sr * Cfg::kRawBytes);
       uint8_t *vst = v_s + s * kTcVBytes;
       if (OCB_TC_ABLATE & 4) {
       } else if (DT == kTcBf16) {
@@ -314,17 +324,21 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
       fence_proxy_async_smem();          // V is read by the tensor core through the async proxy
       __syncwarp();
       if (lane == 0) {
-        mbar_arrive(smem_u32(raw_empty + s));
+        mbar_arrive(smem_u32(raw_empty + sr));
         mbar_arrive(smem_u32(v_ready + s));
       }
     }
-  } else if (warp == 5) {
-    // ===================================== MMA issuer ==========================================
-    // One thread issues.  Its instruction stream is the limit for these small MMAs (N = 32 costs
-    // the tensor pipe ~50 cycles), so the descriptors are built once and only advanced by
-    // constants inside the fully unrolled loop: building them per instruction made each MMA cost
-    // ~180 cycles.
+  } else if (warp == 5 || warp == kTcMmaWarpB) {
+    // ===================================== MMA issuers =========================================
+    // Two threads, each issuing the MMAs of eight positions (disjoint accumulator columns, so no
+    // ordering is needed between them).  One thread's waits and fences then overlap the other's
+    // issuing; with a single issuer its instruction stream (16 MMAs plus ~500 cycles of waits,
+    // fence and commit per K-step) was what bounded the main loop.
+    // The descriptors are built once and only advanced by constants inside the fully unrolled
+    // loop: building them per instruction made each of these small MMAs (N = 32 occupies the
+    // tensor pipe ~50 cycles) cost ~180 cycles.
     if (lane == 0) {
+      const int x0 = warp == 5 ? 0 : 8;                                  // first position of this thread
       const uint32_t idesc = instr_desc<DT>();
       // A: 128 filters x KC channels, filter-contiguous rows of 128 B (64 bf16 / 32 tf32 filters), 8-channel
       //    groups 1 KB apart, 128-byte-row blocks of the filter axis KC*128 B apart.
@@ -348,8 +362,10 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
         const uint64_t ad = (dup ? a_desc0_dup : a_desc0) + (uint64_t)(s * (kTcUBytes >> 4)), bd = b_desc0 + (uint64_t)(s * (kTcVBytes >> 4));
         const uint32_t accumulate = ci > 0 ? 1u : 0u;
 #pragma unroll
-        for (int xi = 0; xi < ((OCB_TC_ABLATE & 8) ? 0 : 16); ++xi)
+        for (int xo = 0; xo < ((OCB_TC_ABLATE & 8) ? 0 : 8); ++xo) {
+          const int xi = x0 + xo;
           tc_mma<DT>(tmem_base + xi * kTcN, ad + (uint64_t)(xi * (4096 >> 4)), bd + (uint64_t)(xi * (1024 >> 4)), idesc, accumulate);
+        }
         tc_commit(smem_u32(uv_empty + s));                 // stage reusable when these MMAs are done
         if (++ci == cpt) {
           tc_commit(smem_u32(acc_full));                   // tile finished
