@@ -42,8 +42,9 @@ enum TcType : int { kTcBf16 = 0, kTcTf32 = 1 };
 
 constexpr int kTcEpilogueWarps = 8;
 constexpr int kTcULoaderWarp = 6 + kTcEpilogueWarps;          // warp 14
-constexpr int kTcMmaWarpB = kTcULoaderWarp + 1;               // warp 15: issues the MMAs of positions 8-15
-constexpr int kTcThreads = (kTcMmaWarpB + 1) * 32;
+constexpr int kTcIssuers = 2;                                 // MMA-issuing threads: warp 5 and warps 15.. (four measured the same)
+constexpr int kTcMmaWarpB = kTcULoaderWarp + 1;               // warp 15: first of the additional issuers
+constexpr int kTcThreads = (kTcMmaWarpB + kTcIssuers - 1) * 32;
 constexpr int kTcM = 128;                   // filters per CTA tile
 constexpr int kTcN = 32;                    // images per CTA tile
 constexpr int kTcStages = 2;
@@ -249,9 +250,9 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
     for (int s = 0; s < kTcStages; ++s) {
       mbar_init(smem_u32(u_full + s), 1);
       mbar_init(smem_u32(v_ready + s), 4);
-      mbar_init(smem_u32(uv_empty + s), 2);      // one tcgen05.commit per MMA-issuing thread
+      mbar_init(smem_u32(uv_empty + s), kTcIssuers);      // one tcgen05.commit per MMA-issuing thread
     }
-    mbar_init(smem_u32(acc_full), 2);
+    mbar_init(smem_u32(acc_full), kTcIssuers);
     mbar_init(smem_u32(acc_empty), kTcEpilogueWarps);
     mbar_fence_init();
   }
@@ -328,7 +329,7 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
         mbar_arrive(smem_u32(v_ready + s));
       }
     }
-  } else if (warp == 5 || warp == kTcMmaWarpB) {
+  } else if (warp == 5 || warp >= kTcMmaWarpB) {
     // ===================================== MMA issuers =========================================
     // Two threads, each issuing the MMAs of eight positions (disjoint accumulator columns, so no
     // ordering is needed between them).  One thread's waits and fences then overlap the other's
@@ -338,7 +339,8 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
     // loop: building them per instruction made each of these small MMAs (N = 32 occupies the
     // tensor pipe ~50 cycles) cost ~180 cycles.
     if (lane == 0) {
-      const int x0 = warp == 5 ? 0 : 8;                                  // first position of this thread
+      constexpr int kPer = 16 / kTcIssuers;                              // positions per issuing thread
+      const int x0 = warp == 5 ? 0 : kPer * (warp - kTcMmaWarpB + 1);    // first position of this thread
       const uint32_t idesc = instr_desc<DT>();
       // A: 128 filters x KC channels, filter-contiguous rows of 128 B (64 bf16 / 32 tf32 filters), 8-channel
       //    groups 1 KB apart, 128-byte-row blocks of the filter axis KC*128 B apart.
@@ -362,7 +364,7 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
         const uint64_t ad = (dup ? a_desc0_dup : a_desc0) + (uint64_t)(s * (kTcUBytes >> 4)), bd = b_desc0 + (uint64_t)(s * (kTcVBytes >> 4));
         const uint32_t accumulate = ci > 0 ? 1u : 0u;
 #pragma unroll
-        for (int xo = 0; xo < ((OCB_TC_ABLATE & 8) ? 0 : 8); ++xo) {
+        for (int xo = 0; xo < ((OCB_TC_ABLATE & 8) ? 0 : kPer); ++xo) {
           const int xi = x0 + xo;
           tc_mma<DT>(tmem_base + xi * kTcN, ad + (uint64_t)(xi * (4096 >> 4)), bd + (uint64_t)(xi * (1024 >> 4)), idesc, accumulate);
         }

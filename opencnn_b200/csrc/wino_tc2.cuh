@@ -28,7 +28,8 @@ constexpr int kP2EpilogueWarps = 8;
 constexpr int kP2MmaWarp = 1 + kP2TransformWarps;
 constexpr int kP2FirstEpilogueWarp = kP2MmaWarp + 1;
 constexpr int kP2ULoaderWarp = kP2FirstEpilogueWarp + kP2EpilogueWarps;
-constexpr int kP2Threads = (kP2ULoaderWarp + 1) * 32;
+constexpr int kP2MmaWarpB = kP2ULoaderWarp + 1;   // second MMA-issuing thread (positions 4-7 of the CTA's eight)
+constexpr int kP2Threads = (kP2MmaWarpB + 1) * 32;
 constexpr uint32_t kP2UBytes = 8 * 4096;         // 8 positions x (128 filters x one K-step)
 constexpr uint32_t kP2VBytes = 8 * 2048;         // 8 positions x (64 images x one K-step)
 
@@ -184,11 +185,11 @@ __device__ __forceinline__ void p2_body(const CUtensorMap &tm_in, const CUtensor
       mbar_init(smem_u32(raw_empty + s), kP2TransformWarps);
       mbar_init(smem_u32(u_full + s), 1);
       mbar_init(smem_u32(v_ready + s), kP2TransformWarps);
-      mbar_init(smem_u32(uv_empty + s), 1);
+      mbar_init(smem_u32(uv_empty + s), 2);      // one tcgen05.commit per MMA-issuing thread
     }
     mbar_init(smem_u32(peer_ready + 0), kP2EpilogueWarps);
     mbar_init(smem_u32(peer_ready + 1), kP2EpilogueWarps);
-    mbar_init(smem_u32(acc_full), 1);
+    mbar_init(smem_u32(acc_full), 2);
     mbar_init(smem_u32(acc_empty), kP2EpilogueWarps);
     mbar_fence_init();
   }
@@ -251,9 +252,10 @@ __device__ __forceinline__ void p2_body(const CUtensorMap &tm_in, const CUtensor
         mbar_arrive(smem_u32(v_ready + s));
       }
     }
-  } else if (warp == kP2MmaWarp) {
-    // ===================================== MMA issuer ==========================================
+  } else if (warp == kP2MmaWarp || warp == kP2MmaWarpB) {
+    // ===================================== MMA issuers (two threads, four positions each; see wino_tc.cuh) ====
     if (lane == 0) {
+      const int x0 = warp == kP2MmaWarp ? 0 : 4;
       const uint32_t fmt = DT == kTcBf16 ? 1u : 2u;
       const uint32_t idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (1u << 15) | (1u << 16) |
                              ((uint32_t)(kP2N >> 3) << 17) | ((uint32_t)(kTcM >> 4) << 24);
@@ -272,8 +274,10 @@ __device__ __forceinline__ void p2_body(const CUtensorMap &tm_in, const CUtensor
         const uint64_t ad = a_desc0 + (uint64_t)(s * (kP2UBytes >> 4)), bd = b_desc0 + (uint64_t)(s * (kP2VBytes >> 4));
         const uint32_t accumulate = ci > 0 ? 1u : 0u;
 #pragma unroll
-        for (int xl = 0; xl < 8; ++xl)
+        for (int xo = 0; xo < 4; ++xo) {
+          const int xl = x0 + xo;
           tc_mma<DT>(tmem_base + xl * kP2N, ad + (uint64_t)(xl * (4096 >> 4)), bd + (uint64_t)(xl * (2048 >> 4)), idesc, accumulate);
+        }
         tc_commit(smem_u32(uv_empty + s));
         if (++ci == cpt) {
           tc_commit(smem_u32(acc_full));

@@ -14,10 +14,11 @@ from opencnn_b200 import api  # noqa: E402
 
 pytestmark = pytest.mark.gpu
 
-# the last three have >= 32 K-steps per tile and >= 64 images: they take the CTA-pair kernel (also with an odd
-# number of 32-image blocks and with K not a multiple of 128); the others take the single-CTA kernel
+# Problems with >= 64 K-steps per tile (C >= 512 in TF32, C >= 1024 in BF16) and >= 64 images take the CTA-pair
+# kernel - the last five here, also with an odd number of 32-image blocks and with K not a multiple of 128 -, the
+# others the single-CTA kernel.
 SHAPES = [(32, 16, 128, 8, 8), (32, 8, 64, 7, 7), (64, 40, 192, 5, 9), (32, 64, 64, 14, 14), (96, 32, 256, 6, 6),
-          (64, 512, 128, 4, 4), (96, 512, 192, 3, 5), (128, 520, 64, 2, 2)]
+          (64, 512, 128, 4, 4), (96, 512, 192, 3, 5), (128, 520, 64, 2, 2), (64, 1024, 128, 3, 3), (96, 1040, 192, 2, 3)]
 MODEL_REL = 2e-4                     # device vs model: fp32 accumulation order inside the tensor core
 TRUTH_REL = {"tf32": 4e-3, "bf16": 3e-2}   # device vs fp64 truth, relative to rms(truth)
 
@@ -54,8 +55,9 @@ def test_tensor_core_path(oracle, libs, precision, shape):
     assert tworst <= TRUTH_REL[precision] * trms, f"vs fp64: {tworst / trms:.3e} of rms"
 
 
-# Ragged last image block (N % 8 == 0 on this path), single-CTA kernel and CTA-pair kernel (>= 32 K-steps, N >= 64).
+# Ragged last image block (N % 8 == 0 on this path), single-CTA kernel and CTA-pair kernel (>= 64 K-steps, N >= 64).
 RAGGED = [(40, 16, 128, 6, 6), (72, 32, 64, 5, 7), (8, 16, 128, 4, 4), (72, 512, 128, 4, 4), (104, 512, 128, 3, 3),
+          (72, 1024, 128, 2, 2),
           (32, 3, 64, 6, 6), (40, 21, 128, 5, 5), (64, 515, 128, 3, 3)]   # and channel counts that are not a multiple of 8
 
 
