@@ -404,6 +404,7 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
       // this warp's share of the 32 images: image quads jbase .. jbase + iters - 1
       const int iters = (OCB_TC_ABLATE & 16) ? 0 : (dup ? 2 : 4);
       const int jbase = dup ? 2 * (2 * (quarter >> 1) + sub) : 4 * sub;
+      bool released = false;
 #pragma unroll 1
       for (int jj = 0; jj < iters; jj += 2) {
         if (!warp_valid) break;
@@ -417,6 +418,14 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
 #pragma unroll
           for (int xi = 0; xi < 16; ++xi) tmem_ld_x4(tlane + xi * kTcN + 4 * j, mm[xi]);
           tmem_ld_wait();
+          if (h2 == 1 && jj + 2 >= iters) {
+            // That was this warp's last read of the accumulators: hand them back before the
+            // arithmetic and the stores of the last step, so the next tile's MMAs start earlier.
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(acc_empty));
+            released = true;
+          }
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             float col[16], yy[4];
@@ -438,9 +447,11 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
           }
         }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(acc_empty));
+      if (!released) {                       // warps without valid filters, or ablated epilogue
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(acc_empty));
+      }
     }
   }
 
