@@ -65,12 +65,8 @@ __device__ __forceinline__ void red_global_add_v4(float *p, const float (&a)[4])
 // BF16: item = (channel c, image pair np of 32); V tile of a position is [16 c][64 n] bf16, rows of
 // 128 bytes, 128-byte swizzle.
 template <int RANK>
-__device__ __forceinline__ void p2_transform_bf16(const float *__restrict__ raw, uint8_t *__restrict__ vst, int c, int np) {
-  const uint64_t *R = reinterpret_cast<const uint64_t *>(raw + (c * 12) * kP2N + 2 * np);
-  constexpr int P = kP2N / 2;
-  uint64_t d[12], b[8];                      // d: patch rows RANK..RANK+2; b: transform rows 2*RANK, 2*RANK+1
-#pragma unroll
-  for (int q = 0; q < 12; ++q) d[q] = R[q * P];
+__device__ __forceinline__ void p2_finish_bf16(const uint64_t (&d)[12], uint8_t *__restrict__ vst, int c, int np) {
+  uint64_t b[8];                             // transform rows 2*RANK, 2*RANK+1 (d: patch rows RANK..RANK+2)
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     if (RANK == 0) {
@@ -97,14 +93,22 @@ __device__ __forceinline__ void p2_transform_bf16(const float *__restrict__ raw,
     }
   }
 }
+// Two items (channels c and c + 8 of image pair np) at once, loads first (see the TF32 version).
+template <int RANK>
+__device__ __forceinline__ void p2_transform_bf16_x2(const float *__restrict__ raw, uint8_t *__restrict__ vst, int c, int np) {
+  const uint64_t *R0 = reinterpret_cast<const uint64_t *>(raw + (c * 12) * kP2N + 2 * np), *R1 = R0 + 8 * 12 * (kP2N / 2);
+  constexpr int P = kP2N / 2;
+  uint64_t d0[12], d1[12];
+#pragma unroll
+  for (int q = 0; q < 12; ++q) { d0[q] = R0[q * P]; d1[q] = R1[q * P]; }
+  p2_finish_bf16<RANK>(d0, vst, c, np);
+  p2_finish_bf16<RANK>(d1, vst, c + 8, np);
+}
 // TF32: item = (channel c, image n of 64); V tile of a position is [2 image blocks][8 c][32 n] fp32,
 // rows of 128 bytes, 128-byte swizzle with 32-byte atoms.
 template <int RANK>
-__device__ __forceinline__ void p2_transform_tf32(const float *__restrict__ raw, uint8_t *__restrict__ vst, int c, int n) {
-  const float *R = raw + (c * 12) * kP2N + n;
-  float d[12], b[8];
-#pragma unroll
-  for (int q = 0; q < 12; ++q) d[q] = R[q * kP2N];
+__device__ __forceinline__ void p2_finish_tf32(const float (&d)[12], uint8_t *__restrict__ vst, int c, int n) {
+  float b[8];
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     if (RANK == 0) {
@@ -127,6 +131,17 @@ __device__ __forceinline__ void p2_transform_tf32(const float *__restrict__ raw,
 #pragma unroll
     for (int j = 0; j < 4; ++j) *reinterpret_cast<float *>(dst + (4 * ii + j) * 2048) = round_tf32_rne(o[j]);
   }
+}
+// Two items (channels c and c + 4 of image n) at once: all 24 loads are issued before any
+// arithmetic, so the two shared-memory round trips overlap.
+template <int RANK>
+__device__ __forceinline__ void p2_transform_tf32_x2(const float *__restrict__ raw, uint8_t *__restrict__ vst, int c, int n) {
+  const float *R0 = raw + (c * 12) * kP2N + n, *R1 = R0 + 4 * 12 * kP2N;
+  float d0[12], d1[12];
+#pragma unroll
+  for (int q = 0; q < 12; ++q) { d0[q] = R0[q * kP2N]; d1[q] = R1[q * kP2N]; }
+  p2_finish_tf32<RANK>(d0, vst, c, n);
+  p2_finish_tf32<RANK>(d1, vst, c + 4, n);
 }
 
 // Partial output transform of one (filter, image) from the 8 positions of rows 2*RANK, 2*RANK+1:
@@ -239,11 +254,9 @@ __device__ __forceinline__ void p2_body(const CUtensorMap &tm_in, const CUtensor
       const float *__restrict__ raw = reinterpret_cast<const float *>(raw_s + s * Cfg::kRawBytes);
       uint8_t *__restrict__ vst = v_s + s * kP2VBytes;
       if (DT == kTcBf16) {
-        p2_transform_bf16<RANK>(raw, vst, t >> 5, t & 31);
-        p2_transform_bf16<RANK>(raw, vst, (t >> 5) + 8, t & 31);
+        p2_transform_bf16_x2<RANK>(raw, vst, t >> 5, t & 31);
       } else {
-        p2_transform_tf32<RANK>(raw, vst, t >> 6, t & 63);
-        p2_transform_tf32<RANK>(raw, vst, (t >> 6) + 4, t & 63);
+        p2_transform_tf32_x2<RANK>(raw, vst, t >> 6, t & 63);
       }
       fence_proxy_async_smem();          // V is read by the tensor core through the async proxy
       __syncwarp();
