@@ -157,12 +157,8 @@ __global__ void __launch_bounds__(128) fx_tc_kernel(const float4 *__restrict__ g
 // ---- input transform into the V operand --------------------------------------------------------
 // BF16: item = (channel c of the stage, image pair np); V tile of a position is [16 c][32 n] bf16,
 // rows of 64 bytes, 64-byte swizzle (16-byte chunk index ^= (c >> 1) & 3).
-__device__ __forceinline__ void transform_to_v_bf16(const float *raw, uint8_t *vst, int c, int np) {
-  const uint64_t *R = reinterpret_cast<const uint64_t *>(raw + (c * 16) * kTcN + 2 * np);
-  constexpr int P = kTcN / 2;
-  uint64_t d[16], b[16];
-#pragma unroll
-  for (int q = 0; q < 16; ++q) d[q] = R[q * P];
+__device__ __forceinline__ void finish_v_bf16(const uint64_t (&d)[16], uint8_t *__restrict__ vst, int c, int np) {
+  uint64_t b[16];
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     b[j] = sub2(d[j], d[8 + j]);
@@ -186,14 +182,22 @@ __device__ __forceinline__ void transform_to_v_bf16(const float *raw, uint8_t *v
     }
   }
 }
+// The two items of a thread (channels c and c + 8 of image pair np): all loads first, so that
+// the two shared-memory round trips overlap.
+__device__ __forceinline__ void transform_to_v_bf16_x2(const float *__restrict__ raw, uint8_t *__restrict__ vst, int c, int np) {
+  constexpr int P = kTcN / 2;
+  const uint64_t *R0 = reinterpret_cast<const uint64_t *>(raw + (c * 16) * kTcN + 2 * np), *R1 = R0 + 8 * 16 * P;
+  uint64_t d0[16], d1[16];
+#pragma unroll
+  for (int q = 0; q < 16; ++q) { d0[q] = R0[q * P]; d1[q] = R1[q * P]; }
+  finish_v_bf16(d0, vst, c, np);
+  finish_v_bf16(d1, vst, c + 8, np);
+}
 // TF32: item = (channel c of the stage, image n); V tile of a position is [8 c][32 n] fp32, rows
 // of 128 bytes, in the "128-byte swizzle with 32-byte atoms" pattern that MN-major 32-bit operands
 // need (32-byte chunk index ^= c & 3; the pattern repeats every 4 rows).
-__device__ __forceinline__ void transform_to_v_tf32(const float *raw, uint8_t *vst, int c, int n) {
-  const float *R = raw + (c * 16) * kTcN + n;
-  float d[16], b[16];
-#pragma unroll
-  for (int q = 0; q < 16; ++q) d[q] = R[q * kTcN];
+__device__ __forceinline__ void finish_v_tf32(const float (&d)[16], uint8_t *__restrict__ vst, int c, int n) {
+  float b[16];
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
     b[j] = __fsub_rn(d[j], d[8 + j]);
@@ -212,6 +216,15 @@ __device__ __forceinline__ void transform_to_v_tf32(const float *raw, uint8_t *v
 #pragma unroll
     for (int j = 0; j < 4; ++j) *reinterpret_cast<float *>(dst + (4 * i + j) * 1024) = round_tf32_rne(o[j]);
   }
+}
+// The two items of a thread (channels c and c + 4 of image n), loads first.
+__device__ __forceinline__ void transform_to_v_tf32_x2(const float *__restrict__ raw, uint8_t *__restrict__ vst, int c, int n) {
+  const float *R0 = raw + (c * 16) * kTcN + n, *R1 = R0 + 4 * 16 * kTcN;
+  float d0[16], d1[16];
+#pragma unroll
+  for (int q = 0; q < 16; ++q) { d0[q] = R0[q * kTcN]; d1[q] = R1[q * kTcN]; }
+  finish_v_tf32(d0, vst, c, n);
+  finish_v_tf32(d1, vst, c + 4, n);
 }
 
 // True when the tile's accumulator rows 64-127 repeat rows 0-63 (see the MMA issuer).
@@ -316,11 +329,9 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
       uint8_t *vst = v_s + s * kTcVBytes;
       if (OCB_TC_ABLATE & 4) {
       } else if (DT == kTcBf16) {
-        transform_to_v_bf16(raw, vst, t >> 4, t & 15);
-        transform_to_v_bf16(raw, vst, (t >> 4) + 8, t & 15);
+        transform_to_v_bf16_x2(raw, vst, t >> 4, t & 15);
       } else {
-        transform_to_v_tf32(raw, vst, t >> 5, t & 31);
-        transform_to_v_tf32(raw, vst, (t >> 5) + 4, t & 31);
+        transform_to_v_tf32_x2(raw, vst, t >> 5, t & 31);
       }
       fence_proxy_async_smem();          // V is read by the tensor core through the async proxy
       __syncwarp();
