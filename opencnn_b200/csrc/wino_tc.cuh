@@ -13,17 +13,17 @@
 // Both operands are "MN-major" in shared memory (M resp. N contiguous), which is how they exist
 // anyway: U rows of consecutive filters come straight from the transformed-filter workspace by
 // TMA (128-byte swizzle), V rows of consecutive images are written by the transform threads.
-// Per K-step (16 channels in BF16, 8 in TF32) one elected thread issues 16 MMAs.
+// Per K-step (16 channels in BF16, 8 in TF32) two threads issue 8 MMAs each.
 //
-// Warp roles (320 threads):
-//   warp 0      TMA: raw input patches (4-D box, hardware zero-fill = halo)
+// Warp roles (512 threads):
+//   warp 0      TMA: raw input patches (4-D box, hardware zero-fill = halo), a ring of their own
 //   warp 14     TMA: U slices (a loader of its own, so patches never queue behind filter slices)
 //   warps 1-4   input transform B^T d B in fp32, rounding, V written in the UMMA layout
-//   warp 5      MMA issue, tcgen05.commit to free stages and to publish a finished tile;
-//               also owns the TMEM allocation
+//   warps 5,15  MMA issue (one thread each, positions 0-7 and 8-15), tcgen05.commit to free stages
+//               and to publish a finished tile; warp 5 also owns the TMEM allocation
 //   warps 6-13  epilogue, two warps per TMEM lane quarter (each takes half of the 32 images):
 //               tcgen05.ld the 16 positions of (filter = TMEM lane, 4 images), A^T M A in
-//               registers - no shared-memory transpose - 16-byte stores
+//               registers - no shared-memory transpose - 32-byte stores
 // All hand-offs are mbarriers with bounded waits.
 #pragma once
 #include "fx.cuh"
@@ -41,9 +41,16 @@ namespace ocb {
 enum TcType : int { kTcBf16 = 0, kTcTf32 = 1 };
 
 constexpr int kTcEpilogueWarps = 8;
-constexpr int kTcULoaderWarp = 6 + kTcEpilogueWarps;          // warp 14
+// Four transform warps, two items per thread and K-step.  Eight warps with one item each were
+// measured too: the CTA then has 640 threads, the register cap drops to 96 and the epilogue
+// spills - 3-5 % slower.  Two groups of two warps taking K-steps alternately were 8 % slower
+// (the transform's latency per K-step matters, not only its throughput).
+constexpr int kTcTransformWarps = 4;                          // warps 1 .. kTcTransformWarps
+constexpr int kTcMmaWarp = 1 + kTcTransformWarps;             // first MMA-issuing thread (also owns the TMEM allocation)
+constexpr int kTcFirstEpilogueWarp = kTcMmaWarp + 1;
+constexpr int kTcULoaderWarp = kTcFirstEpilogueWarp + kTcEpilogueWarps;
 constexpr int kTcIssuers = 2;                                 // MMA-issuing threads: warp 5 and warps 15.. (four measured the same)
-constexpr int kTcMmaWarpB = kTcULoaderWarp + 1;               // warp 15: first of the additional issuers
+constexpr int kTcMmaWarpB = kTcULoaderWarp + 1;               // first of the additional issuers
 constexpr int kTcThreads = (kTcMmaWarpB + kTcIssuers - 1) * 32;
 constexpr int kTcM = 128;                   // filters per CTA tile
 constexpr int kTcN = 32;                    // images per CTA tile
@@ -182,6 +189,14 @@ __device__ __forceinline__ void finish_v_bf16(const uint64_t (&d)[16], uint8_t *
     }
   }
 }
+__device__ __forceinline__ void transform_to_v_bf16(const float *__restrict__ raw, uint8_t *__restrict__ vst, int c, int np) {
+  constexpr int P = kTcN / 2;
+  const uint64_t *R = reinterpret_cast<const uint64_t *>(raw + (c * 16) * kTcN + 2 * np);
+  uint64_t d[16];
+#pragma unroll
+  for (int q = 0; q < 16; ++q) d[q] = R[q * P];
+  finish_v_bf16(d, vst, c, np);
+}
 // The two items of a thread (channels c and c + 8 of image pair np): all loads first, so that
 // the two shared-memory round trips overlap.
 __device__ __forceinline__ void transform_to_v_bf16_x2(const float *__restrict__ raw, uint8_t *__restrict__ vst, int c, int np) {
@@ -216,6 +231,13 @@ __device__ __forceinline__ void finish_v_tf32(const float (&d)[16], uint8_t *__r
 #pragma unroll
     for (int j = 0; j < 4; ++j) *reinterpret_cast<float *>(dst + (4 * i + j) * 1024) = round_tf32_rne(o[j]);
   }
+}
+__device__ __forceinline__ void transform_to_v_tf32(const float *__restrict__ raw, uint8_t *__restrict__ vst, int c, int n) {
+  const float *R = raw + (c * 16) * kTcN + n;
+  float d[16];
+#pragma unroll
+  for (int q = 0; q < 16; ++q) d[q] = R[q * kTcN];
+  finish_v_tf32(d, vst, c, n);
 }
 // The two items of a thread (channels c and c + 4 of image n), loads first.
 __device__ __forceinline__ void transform_to_v_tf32_x2(const float *__restrict__ raw, uint8_t *__restrict__ vst, int c, int n) {
@@ -258,18 +280,18 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
     *dead = 0;
     for (int s = 0; s < SR; ++s) {
       mbar_init(smem_u32(raw_full + s), 1);
-      mbar_init(smem_u32(raw_empty + s), 4);
+      mbar_init(smem_u32(raw_empty + s), kTcTransformWarps);
     }
     for (int s = 0; s < kTcStages; ++s) {
       mbar_init(smem_u32(u_full + s), 1);
-      mbar_init(smem_u32(v_ready + s), 4);
+      mbar_init(smem_u32(v_ready + s), kTcTransformWarps);
       mbar_init(smem_u32(uv_empty + s), kTcIssuers);      // one tcgen05.commit per MMA-issuing thread
     }
     mbar_init(smem_u32(acc_full), kTcIssuers);
     mbar_init(smem_u32(acc_empty), kTcEpilogueWarps);
     mbar_fence_init();
   }
-  if (warp == 5) tmem_alloc_512(smem_u32(tmem_slot));
+  if (warp == kTcMmaWarp) tmem_alloc_512(smem_u32(tmem_slot));
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -317,9 +339,9 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
         }
       }
     }
-  } else if (warp <= 4) {
+  } else if (warp <= kTcTransformWarps) {
     // ===================================== input transform =====================================
-    const int t = tid - 32;                                            // 0..127
+    const int t = tid - 32;                                            // 0 .. 32 * kTcTransformWarps - 1
     for (int g = 0; g < total_chunks; ++g) {
       const int s = g % kTcStages, sr = g % SR;
       const uint32_t use = g / kTcStages;
@@ -328,7 +350,10 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
       const float *raw = reinterpret_cast<const float *>(raw_s + sr * Cfg::kRawBytes);
       uint8_t *vst = v_s + s * kTcVBytes;
       if (OCB_TC_ABLATE & 4) {
-      } else if (DT == kTcBf16) {
+      } else if (kTcTransformWarps == 8) {                         // one item per thread
+        if (DT == kTcBf16) transform_to_v_bf16(raw, vst, t >> 4, t & 15);
+        else               transform_to_v_tf32(raw, vst, t >> 5, t & 31);
+      } else if (DT == kTcBf16) {                                   // four warps: two items per thread
         transform_to_v_bf16_x2(raw, vst, t >> 4, t & 15);
       } else {
         transform_to_v_tf32_x2(raw, vst, t >> 5, t & 31);
@@ -340,7 +365,7 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
         mbar_arrive(smem_u32(v_ready + s));
       }
     }
-  } else if (warp == 5 || warp >= kTcMmaWarpB) {
+  } else if (warp == kTcMmaWarp || warp >= kTcMmaWarpB) {
     // ===================================== MMA issuers =========================================
     // Two threads, each issuing the MMAs of eight positions (disjoint accumulator columns, so no
     // ordering is needed between them).  One thread's waits and fences then overlap the other's
@@ -351,7 +376,7 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
     // tensor pipe ~50 cycles) cost ~180 cycles.
     if (lane == 0) {
       constexpr int kPer = 16 / kTcIssuers;                              // positions per issuing thread
-      const int x0 = warp == 5 ? 0 : kPer * (warp - kTcMmaWarpB + 1);    // first position of this thread
+      const int x0 = warp == kTcMmaWarp ? 0 : kPer * (warp - kTcMmaWarpB + 1);   // first position of this thread
       const uint32_t idesc = instr_desc<DT>();
       // A: 128 filters x KC channels, filter-contiguous rows of 128 B (64 bf16 / 32 tf32 filters), 8-channel
       //    groups 1 KB apart, 128-byte-row blocks of the filter axis KC*128 B apart.
@@ -391,7 +416,7 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
   } else {
     // ===================================== epilogue ============================================
     const int quarter = warp & 3;                                        // TMEM lanes this warp may read
-    const int sub = (warp - 6) >> 2;                                     // 0 / 1: the two warps of a lane quarter
+    const int sub = (warp - kTcFirstEpilogueWarp) >> 2;                  // 0 / 1: the two warps of a lane quarter
     const size_t plane = (size_t)p.H * p.W * p.N;
     const size_t dW = (size_t)p.N, dH = (size_t)p.W * p.N;
     for (int seq = 0; seq < my_tiles; ++seq) {
@@ -468,7 +493,7 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == kTcMmaWarp) {
     tc_fence_after();
     tmem_dealloc_512(tmem_base);
   }
