@@ -278,7 +278,7 @@ cudaError_t launch_wino_tc(const float *input, const float *workspace, float *ou
   p.chunks_per_tile = (C + KC - 1) / KC;
   p.status = st->status_ptr;
   const int grid = p.total_tiles < st->sm_count ? p.total_tiles : st->sm_count;
-  ocb::wino_tc_kernel<DT><<<grid, ocb::kTcThreads, ocb::TcCfg<DT>::kSmemBytes, stream>>>(tm_in, tm_u, p);
+  ocb::wino_tc_kernel<DT><<<grid, ocb::TcCfg<DT>::kThreads, ocb::TcCfg<DT>::kSmemBytes, stream>>>(tm_in, tm_u, p);
   return cudaGetLastError();
 }
 

@@ -49,21 +49,27 @@ constexpr int kTcTransformWarps = 4;                          // warps 1 .. kTcT
 constexpr int kTcMmaWarp = 1 + kTcTransformWarps;             // first MMA-issuing thread (also owns the TMEM allocation)
 constexpr int kTcFirstEpilogueWarp = kTcMmaWarp + 1;
 constexpr int kTcULoaderWarp = kTcFirstEpilogueWarp + kTcEpilogueWarps;
-constexpr int kTcIssuers = 2;                                 // MMA-issuing threads: warp 5 and warps 15.. (four measured the same)
-constexpr int kTcMmaWarpB = kTcULoaderWarp + 1;               // first of the additional issuers
-constexpr int kTcThreads = (kTcMmaWarpB + kTcIssuers - 1) * 32;
+constexpr int kTcMmaWarpB = kTcULoaderWarp + 1;               // first of the additional MMA-issuing warps
 constexpr int kTcM = 128;                   // filters per CTA tile
 constexpr int kTcN = 32;                    // images per CTA tile
 constexpr int kTcStages = 2;
 constexpr uint32_t kTcUBytes = 16 * 4096;   // 16 positions x (128 filters x one K-step)
 constexpr uint32_t kTcVBytes = 16 * 1024;   // 16 positions x (32 images x one K-step)
 
+#ifndef OCB_TC_ISSUERS_OF
+#define OCB_TC_ISSUERS_OF(DT) ((DT) == kTcBf16 ? 2 : 4)
+#endif
 template <int DT> struct TcCfg {
   static constexpr int kKC = DT == kTcBf16 ? 16 : 8;                 // channels per K-step / stage
   static constexpr uint32_t kRawBytes = kKC * 16 * kTcN * 4;         // [c][h][w][n] fp32
   // The raw patches have their own ring, as deep as shared memory allows next to two stages of U
   // and V: TF32 stages are 16 KB (four fit), BF16 stages 32 KB (two).
   static constexpr int kRawStages = DT == kTcBf16 ? 2 : 4;
+  // MMA-issuing threads (warp kTcMmaWarp and warps kTcMmaWarpB ..).  TF32 has twice the MMAs per
+  // channel, and its transform threads are cheap enough for four issuers to pay (3-5 %); in BF16
+  // four measured the same as two.
+  static constexpr int kIssuers = OCB_TC_ISSUERS_OF(DT);
+  static constexpr int kThreads = (kTcMmaWarpB + kIssuers - 1) * 32;
   static constexpr size_t kSmemBytes = (size_t)kRawStages * kRawBytes + (size_t)kTcStages * (kTcUBytes + kTcVBytes) + 1024;
 };
 
@@ -189,14 +195,6 @@ __device__ __forceinline__ void finish_v_bf16(const uint64_t (&d)[16], uint8_t *
     }
   }
 }
-__device__ __forceinline__ void transform_to_v_bf16(const float *__restrict__ raw, uint8_t *__restrict__ vst, int c, int np) {
-  constexpr int P = kTcN / 2;
-  const uint64_t *R = reinterpret_cast<const uint64_t *>(raw + (c * 16) * kTcN + 2 * np);
-  uint64_t d[16];
-#pragma unroll
-  for (int q = 0; q < 16; ++q) d[q] = R[q * P];
-  finish_v_bf16(d, vst, c, np);
-}
 // The two items of a thread (channels c and c + 8 of image pair np): all loads first, so that
 // the two shared-memory round trips overlap.
 __device__ __forceinline__ void transform_to_v_bf16_x2(const float *__restrict__ raw, uint8_t *__restrict__ vst, int c, int np) {
@@ -211,44 +209,38 @@ __device__ __forceinline__ void transform_to_v_bf16_x2(const float *__restrict__
 // TF32: item = (channel c of the stage, image n); V tile of a position is [8 c][32 n] fp32, rows
 // of 128 bytes, in the "128-byte swizzle with 32-byte atoms" pattern that MN-major 32-bit operands
 // need (32-byte chunk index ^= c & 3; the pattern repeats every 4 rows).
-__device__ __forceinline__ void finish_v_tf32(const float (&d)[16], uint8_t *__restrict__ vst, int c, int n) {
-  float b[16];
+// Packed form: one item = (channel c, image pair np); the two images of a pair are adjacent in a
+// V row, so each result is one 8-byte store.  Same operations per image as the scalar form.
+__device__ __forceinline__ void transform_to_v_tf32_pair(const float *__restrict__ raw, uint8_t *__restrict__ vst, int c, int np) {
+  constexpr int P = kTcN / 2;
+  const uint64_t *R = reinterpret_cast<const uint64_t *>(raw + (c * 16) * kTcN + 2 * np);
+  uint64_t d[16], b[16];
+#pragma unroll
+  for (int q = 0; q < 16; ++q) d[q] = R[q * P];
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
-    b[j] = __fsub_rn(d[j], d[8 + j]);
-    b[4 + j] = __fadd_rn(d[4 + j], d[8 + j]);
-    b[8 + j] = __fsub_rn(d[8 + j], d[4 + j]);
-    b[12 + j] = __fsub_rn(d[4 + j], d[12 + j]);
+    b[j] = sub2(d[j], d[8 + j]);
+    b[4 + j] = add2(d[4 + j], d[8 + j]);
+    b[8 + j] = sub2(d[8 + j], d[4 + j]);
+    b[12 + j] = sub2(d[4 + j], d[12 + j]);
   }
+  const int n = 2 * np;
   uint8_t *dst = vst + c * 128 + ((((n >> 3) ^ c) & 3) << 5) + ((n & 7) << 2);
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    float o[4];
-    o[0] = __fsub_rn(b[4 * i + 0], b[4 * i + 2]);
-    o[1] = __fadd_rn(b[4 * i + 1], b[4 * i + 2]);
-    o[2] = __fsub_rn(b[4 * i + 2], b[4 * i + 1]);
-    o[3] = __fsub_rn(b[4 * i + 1], b[4 * i + 3]);
+    uint64_t o[4];
+    o[0] = sub2(b[4 * i + 0], b[4 * i + 2]);
+    o[1] = add2(b[4 * i + 1], b[4 * i + 2]);
+    o[2] = sub2(b[4 * i + 2], b[4 * i + 1]);
+    o[3] = sub2(b[4 * i + 1], b[4 * i + 3]);
 #pragma unroll
-    for (int j = 0; j < 4; ++j) *reinterpret_cast<float *>(dst + (4 * i + j) * 1024) = round_tf32_rne(o[j]);
+    for (int j = 0; j < 4; ++j) {
+      float lo, hi;
+      unpack2(o[j], lo, hi);
+      *reinterpret_cast<float2 *>(dst + (4 * i + j) * 1024) = make_float2(round_tf32_rne(lo), round_tf32_rne(hi));
+    }
   }
 }
-__device__ __forceinline__ void transform_to_v_tf32(const float *__restrict__ raw, uint8_t *__restrict__ vst, int c, int n) {
-  const float *R = raw + (c * 16) * kTcN + n;
-  float d[16];
-#pragma unroll
-  for (int q = 0; q < 16; ++q) d[q] = R[q * kTcN];
-  finish_v_tf32(d, vst, c, n);
-}
-// The two items of a thread (channels c and c + 4 of image n), loads first.
-__device__ __forceinline__ void transform_to_v_tf32_x2(const float *__restrict__ raw, uint8_t *__restrict__ vst, int c, int n) {
-  const float *R0 = raw + (c * 16) * kTcN + n, *R1 = R0 + 4 * 16 * kTcN;
-  float d0[16], d1[16];
-#pragma unroll
-  for (int q = 0; q < 16; ++q) { d0[q] = R0[q * kTcN]; d1[q] = R1[q * kTcN]; }
-  finish_v_tf32(d0, vst, c, n);
-  finish_v_tf32(d1, vst, c + 4, n);
-}
-
 // True when the tile's accumulator rows 64-127 repeat rows 0-63 (see the MMA issuer).
 template <int DT> __device__ __forceinline__ bool tile_repeats_filters(const WinoParams &p, const TileCoord &tc) {
   return DT == kTcBf16 && p.K - tc.kb * kTcM <= 64;
@@ -256,7 +248,7 @@ template <int DT> __device__ __forceinline__ bool tile_repeats_filters(const Win
 
 // p.k_blocks counts 128-filter blocks here.
 template <int DT>
-__global__ void __launch_bounds__(kTcThreads, 1)
+__global__ void __launch_bounds__(TcCfg<DT>::kThreads, 1)
 wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ CUtensorMap tm_u, const WinoParams p) {
   using Cfg = TcCfg<DT>;
   constexpr int KC = Cfg::kKC;
@@ -285,9 +277,9 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
     for (int s = 0; s < kTcStages; ++s) {
       mbar_init(smem_u32(u_full + s), 1);
       mbar_init(smem_u32(v_ready + s), kTcTransformWarps);
-      mbar_init(smem_u32(uv_empty + s), kTcIssuers);      // one tcgen05.commit per MMA-issuing thread
+      mbar_init(smem_u32(uv_empty + s), Cfg::kIssuers);      // one tcgen05.commit per MMA-issuing thread
     }
-    mbar_init(smem_u32(acc_full), kTcIssuers);
+    mbar_init(smem_u32(acc_full), Cfg::kIssuers);
     mbar_init(smem_u32(acc_empty), kTcEpilogueWarps);
     mbar_fence_init();
   }
@@ -350,13 +342,10 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
       const float *raw = reinterpret_cast<const float *>(raw_s + sr * Cfg::kRawBytes);
       uint8_t *vst = v_s + s * kTcVBytes;
       if (OCB_TC_ABLATE & 4) {
-      } else if (kTcTransformWarps == 8) {                         // one item per thread
-        if (DT == kTcBf16) transform_to_v_bf16(raw, vst, t >> 4, t & 15);
-        else               transform_to_v_tf32(raw, vst, t >> 5, t & 31);
-      } else if (DT == kTcBf16) {                                   // four warps: two items per thread
-        transform_to_v_bf16_x2(raw, vst, t >> 4, t & 15);
+      } else if (DT == kTcBf16) {
+        transform_to_v_bf16_x2(raw, vst, t >> 4, t & 15);          // 16 channels x 16 image pairs, two items per thread
       } else {
-        transform_to_v_tf32_x2(raw, vst, t >> 5, t & 31);
+        transform_to_v_tf32_pair(raw, vst, t >> 4, t & 15);        // 8 channels x 16 image pairs = 128 threads
       }
       fence_proxy_async_smem();          // V is read by the tensor core through the async proxy
       __syncwarp();
@@ -375,7 +364,7 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
     // loop: building them per instruction made each of these small MMAs (N = 32 occupies the
     // tensor pipe ~50 cycles) cost ~180 cycles.
     if (lane == 0) {
-      constexpr int kPer = 16 / kTcIssuers;                              // positions per issuing thread
+      constexpr int kPer = 16 / Cfg::kIssuers;                              // positions per issuing thread
       const int x0 = warp == kTcMmaWarp ? 0 : kPer * (warp - kTcMmaWarpB + 1);   // first position of this thread
       const uint32_t idesc = instr_desc<DT>();
       // A: 128 filters x KC channels, filter-contiguous rows of 128 B (64 bf16 / 32 tf32 filters), 8-channel

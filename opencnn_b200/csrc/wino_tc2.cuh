@@ -132,6 +132,42 @@ __device__ __forceinline__ void p2_finish_tf32(const float (&d)[12], uint8_t *__
     for (int j = 0; j < 4; ++j) *reinterpret_cast<float *>(dst + (4 * ii + j) * 2048) = round_tf32_rne(o[j]);
   }
 }
+// Packed form: one item = (channel c, image pair np of 32); the two images of a pair are adjacent
+// in a V row, so each result is one 8-byte store.
+template <int RANK>
+__device__ __forceinline__ void p2_transform_tf32_pair(const float *__restrict__ raw, uint8_t *__restrict__ vst, int c, int np) {
+  const uint64_t *R = reinterpret_cast<const uint64_t *>(raw + (c * 12) * kP2N + 2 * np);
+  constexpr int P = kP2N / 2;
+  uint64_t d[12], b[8];
+#pragma unroll
+  for (int q = 0; q < 12; ++q) d[q] = R[q * P];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (RANK == 0) {
+      b[j] = sub2(d[j], d[8 + j]);
+      b[4 + j] = add2(d[4 + j], d[8 + j]);
+    } else {
+      b[j] = sub2(d[4 + j], d[j]);
+      b[4 + j] = sub2(d[j], d[8 + j]);
+    }
+  }
+  const int n = 2 * np, nl = n & 31;
+  uint8_t *dst = vst + (n >> 5) * 1024 + c * 128 + ((((nl >> 3) ^ c) & 3) << 5) + ((nl & 7) << 2);
+#pragma unroll
+  for (int ii = 0; ii < 2; ++ii) {
+    uint64_t o[4];
+    o[0] = sub2(b[4 * ii + 0], b[4 * ii + 2]);
+    o[1] = add2(b[4 * ii + 1], b[4 * ii + 2]);
+    o[2] = sub2(b[4 * ii + 2], b[4 * ii + 1]);
+    o[3] = sub2(b[4 * ii + 1], b[4 * ii + 3]);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      float lo, hi;
+      unpack2(o[j], lo, hi);
+      *reinterpret_cast<float2 *>(dst + (4 * ii + j) * 2048) = make_float2(round_tf32_rne(lo), round_tf32_rne(hi));
+    }
+  }
+}
 // Two items (channels c and c + 4 of image n) at once: all 24 loads are issued before any
 // arithmetic, so the two shared-memory round trips overlap.
 template <int RANK>
@@ -256,7 +292,7 @@ __device__ __forceinline__ void p2_body(const CUtensorMap &tm_in, const CUtensor
       if (DT == kTcBf16) {
         p2_transform_bf16_x2<RANK>(raw, vst, t >> 5, t & 31);
       } else {
-        p2_transform_tf32_x2<RANK>(raw, vst, t >> 6, t & 63);
+        p2_transform_tf32_pair<RANK>(raw, vst, t >> 5, t & 31);   // 8 channels x 32 image pairs = 256 threads
       }
       fence_proxy_async_smem();          // V is read by the tensor core through the async proxy
       __syncwarp();
