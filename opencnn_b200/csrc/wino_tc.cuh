@@ -13,13 +13,13 @@
 // Both operands are "MN-major" in shared memory (M resp. N contiguous), which is how they exist
 // anyway: U rows of consecutive filters come straight from the transformed-filter workspace by
 // TMA (128-byte swizzle), V rows of consecutive images are written by the transform threads.
-// Per K-step (16 channels in BF16, 8 in TF32) two threads issue 8 MMAs each.
+// Per K-step (16 channels in BF16, 8 in TF32) 16 MMAs are issued, by two threads in BF16 and four in TF32.
 //
-// Warp roles (512 threads):
+// Warp roles (512 threads in BF16, 576 in TF32):
 //   warp 0      TMA: raw input patches (4-D box, hardware zero-fill = halo), a ring of their own
 //   warp 14     TMA: U slices (a loader of its own, so patches never queue behind filter slices)
 //   warps 1-4   input transform B^T d B in fp32, rounding, V written in the UMMA layout
-//   warps 5,15  MMA issue (one thread each, positions 0-7 and 8-15), tcgen05.commit to free stages
+//   warps 5,15+ MMA issue (one thread each, 8 or 4 positions per thread), tcgen05.commit to free stages
 //               and to publish a finished tile; warp 5 also owns the TMEM allocation
 //   warps 6-13  epilogue, two warps per TMEM lane quarter (each takes half of the 32 images):
 //               tcgen05.ld the 16 positions of (filter = TMEM lane, 4 images), A^T M A in
@@ -56,9 +56,6 @@ constexpr int kTcStages = 2;
 constexpr uint32_t kTcUBytes = 16 * 4096;   // 16 positions x (128 filters x one K-step)
 constexpr uint32_t kTcVBytes = 16 * 1024;   // 16 positions x (32 images x one K-step)
 
-#ifndef OCB_TC_ISSUERS_OF
-#define OCB_TC_ISSUERS_OF(DT) ((DT) == kTcBf16 ? 2 : 4)
-#endif
 template <int DT> struct TcCfg {
   static constexpr int kKC = DT == kTcBf16 ? 16 : 8;                 // channels per K-step / stage
   static constexpr uint32_t kRawBytes = kKC * 16 * kTcN * 4;         // [c][h][w][n] fp32
@@ -68,7 +65,7 @@ template <int DT> struct TcCfg {
   // MMA-issuing threads (warp kTcMmaWarp and warps kTcMmaWarpB ..).  TF32 has twice the MMAs per
   // channel, and its transform threads are cheap enough for four issuers to pay (3-5 %); in BF16
   // four measured the same as two.
-  static constexpr int kIssuers = OCB_TC_ISSUERS_OF(DT);
+  static constexpr int kIssuers = DT == kTcBf16 ? 2 : 4;
   static constexpr int kThreads = (kTcMmaWarpB + kIssuers - 1) * 32;
   static constexpr size_t kSmemBytes = (size_t)kRawStages * kRawBytes + (size_t)kTcStages * (kTcUBytes + kTcVBytes) + 1024;
 };
