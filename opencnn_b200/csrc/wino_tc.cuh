@@ -255,7 +255,7 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
   uint8_t *u_s = raw_s + SR * Cfg::kRawBytes;                          // [stage][16 xi][...]  4 KB per position
   uint8_t *v_s = u_s + kTcStages * kTcUBytes;                          // [stage][16 xi][...]  1 KB per position
   uint64_t *bars = reinterpret_cast<uint64_t *>(v_s + kTcStages * kTcVBytes);
-  uint64_t *raw_full = bars, *raw_empty = bars + SR, *u_full = bars + 2 * SR, *v_ready = u_full + 2, *uv_empty = u_full + 4;
+  uint64_t *raw_full = bars, *raw_empty = bars + SR, *u_full = bars + 2 * SR, *uv_empty = u_full + 4;   // u_full: U landed and V written
   uint64_t *acc_full = u_full + 6, *acc_empty = u_full + 7;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(u_full + 8);
   volatile int *dead = reinterpret_cast<volatile int *>(u_full + 9);
@@ -272,8 +272,7 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
       mbar_init(smem_u32(raw_empty + s), kTcTransformWarps);
     }
     for (int s = 0; s < kTcStages; ++s) {
-      mbar_init(smem_u32(u_full + s), 1);
-      mbar_init(smem_u32(v_ready + s), kTcTransformWarps);
+      mbar_init(smem_u32(u_full + s), kTcTransformWarps + 1);   // U loader (with its bytes) + one arrive per transform warp
       mbar_init(smem_u32(uv_empty + s), Cfg::kIssuers);      // one tcgen05.commit per MMA-issuing thread
     }
     mbar_init(smem_u32(acc_full), Cfg::kIssuers);
@@ -348,7 +347,7 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
       __syncwarp();
       if (lane == 0) {
         mbar_arrive(smem_u32(raw_empty + sr));
-        mbar_arrive(smem_u32(v_ready + s));
+        mbar_arrive(smem_u32(u_full + s));
       }
     }
   } else if (warp == kTcMmaWarp || warp >= kTcMmaWarpB) {
@@ -379,8 +378,7 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
       for (int g = 0; g < total_chunks; ++g) {
         const int s = g % kTcStages;
         const uint32_t use = g / kTcStages;
-        mbar_wait(smem_u32(u_full + s), use & 1, dead, p.status);
-        mbar_wait(smem_u32(v_ready + s), use & 1, dead, p.status);
+        mbar_wait(smem_u32(u_full + s), use & 1, dead, p.status);      // U landed and V written
         if (ci == 0 && seq > 0) mbar_wait(smem_u32(acc_empty), (seq - 1) & 1, dead, p.status);   // TMEM drained
         tc_fence_after();
         const uint64_t ad = (dup ? a_desc0_dup : a_desc0) + (uint64_t)(s * (kTcUBytes >> 4)), bd = b_desc0 + (uint64_t)(s * (kTcVBytes >> 4));
