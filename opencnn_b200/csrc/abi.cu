@@ -94,6 +94,9 @@ cudaError_t device_state(DeviceState **out) {
       err = cudaFuncSetAttribute(ocb::wino_tc_kernel<ocb::kTcBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)ocb::TcCfg<ocb::kTcBf16>::kSmemBytes);
     if (err == cudaSuccess)
+      err = cudaFuncSetAttribute(ocb::wino_tc_kernel<ocb::kTcBf16, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)ocb::TcCfg<ocb::kTcBf16, true>::kSmemBytes);
+    if (err == cudaSuccess)
       err = cudaFuncSetAttribute(ocb::wino_tc_kernel<ocb::kTcTf32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  (int)ocb::TcCfg<ocb::kTcTf32>::kSmemBytes);
     if (err == cudaSuccess)
@@ -256,7 +259,9 @@ cudaError_t launch_wino_tc(const float *input, const float *workspace, float *ou
     // workspace [C][16][K] viewed as {filter within a 128-byte row, channel, 128-byte row, position}
     cuuint64_t dims[4] = {row_elems, (cuuint64_t)C, (cuuint64_t)K / row_elems, 16};
     cuuint64_t strides[3] = {(cuuint64_t)16 * K * esz, 128, (cuuint64_t)K * esz};
-    cuuint32_t box[4] = {row_elems, (cuuint32_t)KC, (cuuint32_t)(ocb::kTcM / row_elems), 16};
+    // BF16 with at most 64 filters: only the first 64-filter row block is loaded (wino_tc.cuh, "half U")
+    const bool half_u = bf16 && K <= 64;
+    cuuint32_t box[4] = {row_elems, (cuuint32_t)KC, half_u ? 1u : (cuuint32_t)(ocb::kTcM / row_elems), 16};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     if (enc(&tm_u, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4,
             const_cast<float *>(workspace), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -278,7 +283,11 @@ cudaError_t launch_wino_tc(const float *input, const float *workspace, float *ou
   p.chunks_per_tile = (C + KC - 1) / KC;
   p.status = st->status_ptr;
   const int grid = p.total_tiles < st->sm_count ? p.total_tiles : st->sm_count;
-  ocb::wino_tc_kernel<DT><<<grid, ocb::TcCfg<DT>::kThreads, ocb::TcCfg<DT>::kSmemBytes, stream>>>(tm_in, tm_u, p);
+  if (bf16 && K <= 64)
+    ocb::wino_tc_kernel<ocb::kTcBf16, true><<<grid, ocb::TcCfg<ocb::kTcBf16, true>::kThreads,
+                                              ocb::TcCfg<ocb::kTcBf16, true>::kSmemBytes, stream>>>(tm_in, tm_u, p);
+  else
+    ocb::wino_tc_kernel<DT><<<grid, ocb::TcCfg<DT>::kThreads, ocb::TcCfg<DT>::kSmemBytes, stream>>>(tm_in, tm_u, p);
   return cudaGetLastError();
 }
 

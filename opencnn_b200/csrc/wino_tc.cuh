@@ -53,21 +53,26 @@ constexpr int kTcMmaWarpB = kTcULoaderWarp + 1;               // first of the ad
 constexpr int kTcM = 128;                   // filters per CTA tile
 constexpr int kTcN = 32;                    // images per CTA tile
 constexpr int kTcStages = 2;
-constexpr uint32_t kTcUBytes = 16 * 4096;   // 16 positions x (128 filters x one K-step)
 constexpr uint32_t kTcVBytes = 16 * 1024;   // 16 positions x (32 images x one K-step)
 
-template <int DT> struct TcCfg {
+// HU ("half U"): BF16 problems with at most 64 filters.  Their A operand repeats its first
+// 64-filter block (see tile_repeats_filters), so only that block is loaded: U stages are 32 KB
+// instead of 64 KB, and the room goes to the raw-patch ring (four stages instead of two), which
+// is what the large-image layers with few filters lack (their patches come from HBM, not L2).
+template <int DT, bool HU = false> struct TcCfg {
   static constexpr int kKC = DT == kTcBf16 ? 16 : 8;                 // channels per K-step / stage
   static constexpr uint32_t kRawBytes = kKC * 16 * kTcN * 4;         // [c][h][w][n] fp32
   // The raw patches have their own ring, as deep as shared memory allows next to two stages of U
   // and V: TF32 stages are 16 KB (four fit), BF16 stages 32 KB (two).
-  static constexpr int kRawStages = DT == kTcBf16 ? 2 : 4;
+  static constexpr int kRawStages = (DT == kTcBf16 && !HU) ? 2 : 4;
+  static constexpr uint32_t kUPosBytes = HU ? 2048 : 4096;           // one position of a U stage
+  static constexpr uint32_t kUBytes = 16 * kUPosBytes;
   // MMA-issuing threads (warp kTcMmaWarp and warps kTcMmaWarpB ..).  TF32 has twice the MMAs per
   // channel, and its transform threads are cheap enough for four issuers to pay (3-5 %); in BF16
   // four measured the same as two.
   static constexpr int kIssuers = DT == kTcBf16 ? 2 : 4;
   static constexpr int kThreads = (kTcMmaWarpB + kIssuers - 1) * 32;
-  static constexpr size_t kSmemBytes = (size_t)kRawStages * kRawBytes + (size_t)kTcStages * (kTcUBytes + kTcVBytes) + 1024;
+  static constexpr size_t kSmemBytes = (size_t)kRawStages * kRawBytes + (size_t)kTcStages * (kUBytes + kTcVBytes) + 1024;
 };
 
 // ---- tcgen05 wrappers ------------------------------------------------------------------------
@@ -244,16 +249,17 @@ template <int DT> __device__ __forceinline__ bool tile_repeats_filters(const Win
 }
 
 // p.k_blocks counts 128-filter blocks here.
-template <int DT>
-__global__ void __launch_bounds__(TcCfg<DT>::kThreads, 1)
+template <int DT, bool HU = false>
+__global__ void __launch_bounds__(TcCfg<DT, HU>::kThreads, 1)
 wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ CUtensorMap tm_u, const WinoParams p) {
-  using Cfg = TcCfg<DT>;
+  using Cfg = TcCfg<DT, HU>;
+  static_assert(!HU || DT == kTcBf16, "the half-U variant relies on the BF16 block aliasing");
   constexpr int KC = Cfg::kKC;
   extern __shared__ __align__(1024) uint8_t tsmem[];
   uint8_t *raw_s = tsmem;                                              // [stage][KC][16][32] fp32
   constexpr int SR = Cfg::kRawStages;
   uint8_t *u_s = raw_s + SR * Cfg::kRawBytes;                          // [stage][16 xi][...]  4 KB per position
-  uint8_t *v_s = u_s + kTcStages * kTcUBytes;                          // [stage][16 xi][...]  1 KB per position
+  uint8_t *v_s = u_s + kTcStages * Cfg::kUBytes;                       // [stage][16 xi][...]  1 KB per position
   uint64_t *bars = reinterpret_cast<uint64_t *>(v_s + kTcStages * kTcVBytes);
   uint64_t *raw_full = bars, *raw_empty = bars + SR, *u_full = bars + 2 * SR, *uv_empty = u_full + 4;   // u_full: U landed and V written
   uint64_t *acc_full = u_full + 6, *acc_empty = u_full + 7;
@@ -314,9 +320,9 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
           if (OCB_TC_ABLATE & 1) {
             mbar_arrive(smem_u32(u_full + s));
           } else {
-            mbar_arrive_expect_tx(smem_u32(u_full + s), kTcUBytes);
+            mbar_arrive_expect_tx(smem_u32(u_full + s), Cfg::kUBytes);
             // U viewed as {filters within a 128-byte row, channel, 128-byte row of the filter axis, position}
-            tma_load_4d(smem_u32(u_s + s * kTcUBytes), &tm_u, smem_u32(u_full + s), 0, ci * KC,
+            tma_load_4d(smem_u32(u_s + s * Cfg::kUBytes), &tm_u, smem_u32(u_full + s), 0, ci * KC,
                         tc.kb * (DT == kTcBf16 ? 2 : 4), 0);
           }
         }
@@ -381,12 +387,12 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
         mbar_wait(smem_u32(u_full + s), use & 1, dead, p.status);      // U landed and V written
         if (ci == 0 && seq > 0) mbar_wait(smem_u32(acc_empty), (seq - 1) & 1, dead, p.status);   // TMEM drained
         tc_fence_after();
-        const uint64_t ad = (dup ? a_desc0_dup : a_desc0) + (uint64_t)(s * (kTcUBytes >> 4)), bd = b_desc0 + (uint64_t)(s * (kTcVBytes >> 4));
+        const uint64_t ad = ((dup || HU) ? a_desc0_dup : a_desc0) + (uint64_t)(s * (Cfg::kUBytes >> 4)), bd = b_desc0 + (uint64_t)(s * (kTcVBytes >> 4));
         const uint32_t accumulate = ci > 0 ? 1u : 0u;
 #pragma unroll
         for (int xo = 0; xo < ((OCB_TC_ABLATE & 8) ? 0 : kPer); ++xo) {
           const int xi = x0 + xo;
-          tc_mma<DT>(tmem_base + xi * kTcN, ad + (uint64_t)(xi * (4096 >> 4)), bd + (uint64_t)(xi * (1024 >> 4)), idesc, accumulate);
+          tc_mma<DT>(tmem_base + xi * kTcN, ad + (uint64_t)(xi * (Cfg::kUPosBytes >> 4)), bd + (uint64_t)(xi * (1024 >> 4)), idesc, accumulate);
         }
         tc_commit(smem_u32(uv_empty + s));                 // stage reusable when these MMAs are done
         if (++ci == cpt) {
