@@ -158,6 +158,7 @@ def main():
     ap.add_argument("--variant", default="OPTSTS64")
     ap.add_argument("--precision", default="fp32", choices=["fp32", "tf32", "bf16"])
     ap.add_argument("--e2e-steps", type=int, default=20)
+    ap.add_argument("--e2e-depth", type=int, default=3, help="plan sets used in rotation by the end-to-end measurement")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-tensor-core", action="store_true", help="skip the extra TF32/BF16 measurements")
     ap.add_argument("--no-cudnn", action="store_true", help="skip the cuDNN (torch conv2d) baseline")
@@ -395,16 +396,18 @@ def main():
     h2d = sum(hx.numel() * 4 + hg.numel() * 4 for hx, hg, _ in host)
     d2h = sum(hy.numel() * 4 for _, _, hy in host)
     if args.impl == "ours":
-        # Two plans (device buffers + stream) and two host output buffers per layer, used alternately, so
-        # that the uploads of one step overlap the downloads of the step before (PCIe is full duplex).
+        # `depth` plan sets (device buffers + stream) and host output buffers per layer, used in rotation, so
+        # that the uploads of one step overlap the downloads of the steps before (PCIe is full duplex).
         # A plan is waited for before it is used again; the timed region ends after every step has landed.
+        depth = max(1, args.e2e_depth)
         plans = [[api.HostPlan(L["N"], L["C"], L["HW"], L["HW"], L["K"], precision=args.precision, variant=args.variant)
-                  for L in layers] for _ in range(2)]
-        host_out = [[hy for _, _, hy in host], [torch.empty(hy.shape, pin_memory=True) for _, _, hy in host]]
+                  for L in layers] for _ in range(depth)]
+        host_out = [[hy for _, _, hy in host]] + [[torch.empty(hy.shape, pin_memory=True) for _, _, hy in host]
+                                                  for _ in range(depth - 1)]
         e2e_count = [0]
 
         def e2e_step():
-            slot = e2e_count[0] & 1
+            slot = e2e_count[0] % depth
             e2e_count[0] += 1
             for p in plans[slot]:                         # the step two back used this slot: its results must be home
                 if p.wait() != 0:
@@ -414,7 +417,7 @@ def main():
                     raise RuntimeError("host plan failed")
 
         def e2e_drain():
-            for slot in (0, 1):
+            for slot in range(depth):
                 for p in plans[slot]:
                     if p.wait() != 0:
                         raise RuntimeError("host plan failed")
@@ -442,8 +445,8 @@ def main():
     e2e = {"value": flops_step / (e2e_ms * 1e-3) * 1e-12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
            "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": args.e2e_steps,
            "how": "pinned host buffers -> opencnn_host_plan_run_async per layer (H2D, FX, fused kernel, D2H on the "
-                  "plan's stream); two plan sets used alternately so uploads of a step overlap downloads of the "
-                  "previous one; every step's outputs are waited for inside the timed region" if args.impl == "ours" else
+                  "plan's stream); three plan sets used in rotation so uploads of a step overlap downloads of the "
+                  "steps before; every step's outputs are waited for inside the timed region" if args.impl == "ours" else
                   "pinned host buffers; per layer H2D, reference call, D2H on the default stream; one sync per step"}
     if args.impl == "ours":
         for slot in plans:
