@@ -87,3 +87,21 @@ def test_integer_tensors_are_exact_on_tensor_cores(oracle, libs, precision):
     x, g = oracle.input_int(N, C, H, W), oracle.filter_int(C, K)
     y = run_tc(x, g, precision)
     assert np.array_equal(y.astype(np.float64), oracle.direct_f64(x, g))
+
+
+@pytest.mark.parametrize("precision", ["tf32", "bf16"])
+def test_tensor_core_results_are_repeatable(libs, precision):
+    """Same bits run after run, also from the CTA-pair kernel (its two partial results are added by an
+    L2 reduction, but two addends commute)."""
+    for (N, C, K, H, W) in [(64, 64, 64, 9, 9), (64, 1024, 128, 3, 3)]:
+        x = torch.rand((C, H, W, N), device="cuda") * 2 - 1
+        g = torch.randn((C, 3, 3, K), device="cuda") * 0.05
+        ws = torch.empty((C, 4, 4, K), device="cuda")
+        first = torch.empty((K, H, W, N), device="cuda")
+        again = torch.empty_like(first)
+        assert api.conv3x3(x, g, first, ws, N, C, H, W, K, precision=precision) == 0
+        for _ in range(3):
+            assert api.conv3x3(x, g, again, ws, N, C, H, W, K, precision=precision) == 0
+            torch.cuda.synchronize()
+            assert torch.equal(first, again)
+    assert api.last_device_status() == 0
