@@ -349,10 +349,10 @@ cudaError_t launch_wino_tc2(const float *input, const float *workspace, float *o
 
 // Which tensor-core kernel a problem gets.  Both compute the same thing.  The CTA-pair kernel
 // (wino_tc2.cuh) has the cheaper main loop (half as many, twice as wide MMAs) but a dearer
-// epilogue (two CTAs meet through L2), so it wins where a tile has many K-steps.  With two
-// MMA-issuing threads in both kernels it is ahead from 64 K-steps per tile - C >= 512 in TF32
-// (5-20 %), C >= 1024 in BF16 (3 %) - and behind below.  OCB_TC_PAIR forces one of them (0 / 1)
-// for experiments.
+// epilogue (two CTAs meet through L2), so it wins where a tile has many K-steps and the MMAs are
+// many: in TF32 from 64 K-steps per tile (C >= 512: 6-20 % ahead).  In BF16 the single-CTA kernel
+// is level or ahead everywhere since it issues its MMAs from two threads (C = 1024: within 1 %),
+// so BF16 never takes the pair.  OCB_TC_PAIR forces one of them (0 / 1) for experiments.
 template <int DT>
 cudaError_t launch_tc(const float *input, const float *workspace, float *output, int N, int C, int H, int W, int K,
                       cudaStream_t stream) {
@@ -360,7 +360,7 @@ cudaError_t launch_tc(const float *input, const float *workspace, float *output,
   const bool pair = OCB_TC_PAIR != 0;
 #else
   const int k_steps = (C + ocb::TcCfg<DT>::kKC - 1) / ocb::TcCfg<DT>::kKC;
-  const bool pair = k_steps >= 64 && N >= 64;
+  const bool pair = DT == ocb::kTcTf32 && k_steps >= 64 && N >= 64;
 #endif
   return pair ? launch_wino_tc2<DT>(input, workspace, output, N, C, H, W, K, stream)
               : launch_wino_tc<DT>(input, workspace, output, N, C, H, W, K, stream);

@@ -14,9 +14,9 @@ from opencnn_b200 import api  # noqa: E402
 
 pytestmark = pytest.mark.gpu
 
-# Problems with >= 64 K-steps per tile (C >= 512 in TF32, C >= 1024 in BF16) and >= 64 images take the CTA-pair
-# kernel - the last five here, also with an odd number of 32-image blocks and with K not a multiple of 128 -, the
-# others the single-CTA kernel.
+# TF32 problems with >= 64 K-steps per tile (C >= 512) and >= 64 images take the CTA-pair kernel - the last five
+# here, also with an odd number of 32-image blocks and with K not a multiple of 128; everything else, and all of
+# BF16, the single-CTA kernel.
 SHAPES = [(32, 16, 128, 8, 8), (32, 8, 64, 7, 7), (64, 40, 192, 5, 9), (32, 64, 64, 14, 14), (96, 32, 256, 6, 6),
           (64, 512, 128, 4, 4), (96, 512, 192, 3, 5), (128, 520, 64, 2, 2), (64, 1024, 128, 3, 3), (96, 1040, 192, 2, 3)]
 MODEL_REL = 2e-4                     # device vs model: fp32 accumulation order inside the tensor core
@@ -55,7 +55,7 @@ def test_tensor_core_path(oracle, libs, precision, shape):
     assert tworst <= TRUTH_REL[precision] * trms, f"vs fp64: {tworst / trms:.3e} of rms"
 
 
-# Ragged last image block (N % 8 == 0 on this path), single-CTA kernel and CTA-pair kernel (>= 64 K-steps, N >= 64).
+# Ragged last image block (N % 8 == 0 on this path), single-CTA kernel and CTA-pair kernel (TF32, >= 64 K-steps, N >= 64).
 RAGGED = [(40, 16, 128, 6, 6), (72, 32, 64, 5, 7), (8, 16, 128, 4, 4), (72, 512, 128, 4, 4), (104, 512, 128, 3, 3),
           (72, 1024, 128, 2, 2),
           (32, 3, 64, 6, 6), (40, 21, 128, 5, 5), (64, 515, 128, 3, 3)]   # and channel counts that are not a multiple of 8
@@ -91,8 +91,8 @@ def test_integer_tensors_are_exact_on_tensor_cores(oracle, libs, precision):
 
 @pytest.mark.parametrize("precision", ["tf32", "bf16"])
 def test_tensor_core_results_are_repeatable(libs, precision):
-    """Same bits run after run, also from the CTA-pair kernel (its two partial results are added by an
-    L2 reduction, but two addends commute)."""
+    """Same bits run after run, also from the CTA-pair kernel that deep TF32 problems take (its two partial
+    results are added by an L2 reduction, but two addends commute)."""
     for (N, C, K, H, W) in [(64, 64, 64, 9, 9), (64, 1024, 128, 3, 3)]:
         x = torch.rand((C, H, W, N), device="cuda") * 2 - 1
         g = torch.randn((C, 3, 3, K), device="cuda") * 0.05
