@@ -498,9 +498,12 @@ wino_fp32_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constan
           if (c + 1 < kBC) {
             load_frag(frag[(c + 1) & 1], st + voff, st + uoff, o1, c + 1);
           } else {
-            // all reads of this stage are done: hand it back, then look into the next one
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(bar_empty + s));
+            // All reads of this stage have been issued.  With a ring of three stages it is handed
+            // back right away (the look-ahead is short); with four, after the last FMAs (below).
+            if (S < 4) {
+              __syncwarp();
+              if (lane == 0) mbar_arrive(smem_u32(bar_empty + s));
+            }
             if (g + 1 < total_chunks) {
               const int s1 = (g + 1) % S;
               mbar_wait(smem_u32(bar_ready + s1), ((g + 1) / S) & 1, dead, p.status);
@@ -509,6 +512,13 @@ wino_fp32_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constan
             }
           }
           fma_frag(acc, frag[c & 1]);
+        }
+        // Four stages: hand the stage back after the last FMAs rather than before them, so that the
+        // warp-wide synchronisation does not sit in front of an FMA batch (0.5-0.8 % on the sweep;
+        // with three stages the later release costs 2-4 % instead).
+        if (S >= 4) {
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(bar_empty + s));
         }
       }
       const TileCoord tc = decode_tile(p, tile);
