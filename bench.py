@@ -399,15 +399,16 @@ def main():
         # `depth` plan sets (device buffers + stream) and host output buffers per layer, used in rotation, so
         # that the uploads of one step overlap the downloads of the steps before (PCIe is full duplex).
         # A plan is waited for before it is used again; the timed region ends after every step has landed.
-        depth = max(1, args.e2e_depth)
+        max_depth = max(1, args.e2e_depth)
         plans = [[api.HostPlan(L["N"], L["C"], L["HW"], L["HW"], L["K"], precision=args.precision, variant=args.variant)
-                  for L in layers] for _ in range(depth)]
+                  for L in layers] for _ in range(max_depth)]
         host_out = [[hy for _, _, hy in host]] + [[torch.empty(hy.shape, pin_memory=True) for _, _, hy in host]
-                                                  for _ in range(depth - 1)]
+                                                  for _ in range(max_depth - 1)]
         e2e_count = [0]
+        depth_box = [max_depth]          # how many of the sets are in rotation
 
         def e2e_step():
-            slot = e2e_count[0] % depth
+            slot = e2e_count[0] % depth_box[0]
             e2e_count[0] += 1
             for p in plans[slot]:                         # the step two back used this slot: its results must be home
                 if p.wait() != 0:
@@ -417,10 +418,26 @@ def main():
                     raise RuntimeError("host plan failed")
 
         def e2e_drain():
-            for slot in range(depth):
+            for slot in range(max_depth):
                 for p in plans[slot]:
                     if p.wait() != 0:
                         raise RuntimeError("host plan failed")
+
+        # Untimed trial: how many sets to rotate.  One GPU alone is limited by its own PCIe link and gains from
+        # three; several GPUs share the host's copy bandwidth, where a shallower rotation can be as fast or faster.
+        trial = {}
+        for d in range(1, max_depth + 1):
+            depth_box[0] = d
+            for _ in range(2):
+                e2e_step()
+            e2e_drain()
+            sync_all()
+            t0 = time.perf_counter()
+            for _ in range(4):
+                e2e_step()
+            e2e_drain()
+            trial[d] = max_over_ranks(time.perf_counter() - t0)
+        depth_box[0] = min(trial, key=trial.get)       # the same on every rank: the times are maxima over ranks
     else:
         def e2e_step():
             for L, (hx, hg, hy) in zip(layers, host):
@@ -445,9 +462,12 @@ def main():
     e2e = {"value": flops_step / (e2e_ms * 1e-3) * 1e-12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
            "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": args.e2e_steps,
            "how": "pinned host buffers -> opencnn_host_plan_run_async per layer (H2D, FX, fused kernel, D2H on the "
-                  "plan's stream); three plan sets used in rotation so uploads of a step overlap downloads of the "
-                  "steps before; every step's outputs are waited for inside the timed region" if args.impl == "ours" else
+                  "plan's stream); up to three plan sets in rotation (how many is settled by a short untimed trial) so "
+                  "uploads of a step overlap downloads of the steps before; every step's outputs are waited for "
+                  "inside the timed region" if args.impl == "ours" else
                   "pinned host buffers; per layer H2D, reference call, D2H on the default stream; one sync per step"}
+    if args.impl == "ours":
+        e2e["plan_sets_in_rotation"] = depth_box[0]
     if args.impl == "ours":
         for slot in plans:
             for p in slot:
