@@ -14,6 +14,10 @@
  * (N % 4 == 0 with OPENCNN_FP32, N % 8 == 0 with OPENCNN_TF32 / OPENCNN_BF16), any in_c >= 1 and,
  * with OPENCNN_FP32, filt_k % 4 == 0.
  *
+ * Alignment: every device pointer must be 16-byte aligned; with OPENCNN_TF32 / OPENCNN_BF16 the
+ * output must be 32-byte aligned (those kernels store 32 bytes per thread).  cudaMalloc gives
+ * 256.  A pointer that is not is refused with cudaErrorInvalidValue before anything is launched.
+ *
  * Return values are cudaError_t codes passed as int, so the header needs no CUDA include.
  * All pointers are device pointers unless a function says otherwise.  Calls are asynchronous
  * with respect to the host unless a function says otherwise.
@@ -131,6 +135,13 @@ int opencnn_host_plan_run(void *plan, const float *input_host, const float *filt
 int opencnn_host_plan_run_async(void *plan, const float *input_host, const float *filter_host,
                                 float *output_host);
 int opencnn_host_plan_wait(void *plan);
+/* The three copies of opencnn_host_plan_run_async without the kernels between them, on the same
+ * stream: what a step costs when the GPU work is free.  A measurement aid - the floor an
+ * end-to-end time can be compared with; the output buffer receives whatever the plan's device
+ * buffer holds.  The reference's main() has the same copies around its timed loop
+ * (src/openCNN_winograd.cu:300-316, :470-472) and never times them. */
+int opencnn_host_plan_copy_async(void *plan, const float *input_host, const float *filter_host,
+                                 float *output_host);
 int opencnn_host_plan_destroy(void *plan);
 
 #ifdef __cplusplus

@@ -33,6 +33,7 @@ SIGNATURES = {
     "opencnn_host_plan_create": (c_int, [POINTER(c_void_p)] + [c_int] * 6),
     "opencnn_host_plan_run": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p]),
     "opencnn_host_plan_run_async": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p]),
+    "opencnn_host_plan_copy_async": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p]),
     "opencnn_host_plan_wait": (c_int, [c_void_p]),
     "opencnn_host_plan_destroy": (c_int, [c_void_p]),
 }

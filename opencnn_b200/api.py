@@ -127,6 +127,10 @@ class HostPlan:
     def run_async(self, input_host_ptr: int, filter_host_ptr: int, output_host_ptr: int) -> int:
         return self._lib.opencnn_host_plan_run_async(self._h, input_host_ptr, filter_host_ptr, output_host_ptr)
 
+    def copy_async(self, input_host_ptr: int, filter_host_ptr: int, output_host_ptr: int) -> int:
+        """The copies of run_async without the kernels (the end-to-end floor of a step)."""
+        return self._lib.opencnn_host_plan_copy_async(self._h, input_host_ptr, filter_host_ptr, output_host_ptr)
+
     def wait(self) -> int:
         return self._lib.opencnn_host_plan_wait(self._h)
 

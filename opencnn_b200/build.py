@@ -98,11 +98,30 @@ def build_smem_probe(force: bool = False) -> str:
     return target
 
 
+def cudnn_probe_path() -> str:
+    return os.path.join(LIBDIR, "cudnn_probe")
+
+
+def build_cudnn_probe(force: bool = False) -> str | None:
+    """The cuDNN legacy-API timing program (csrc/cudnn_probe.cu), a baseline for bench.py; not part of
+    the operator.  Returns None where cuDNN's headers or library are not installed."""
+    os.makedirs(LIBDIR, exist_ok=True)
+    target, src = cudnn_probe_path(), os.path.join(CSRC, "cudnn_probe.cu")
+    if force or not os.path.exists(target) or os.path.getmtime(src) > os.path.getmtime(target):
+        cmd = [nvcc(), *ARCH, "-O2", "-std=c++17", "-o", target, src, "-lcudnn"]
+        res = subprocess.run(cmd, capture_output=True, text=True)
+        if res.returncode != 0:
+            return None
+    return target
+
+
 def build_all(force: bool = False, verbose: bool = False) -> list[str]:
     with ThreadPoolExecutor(max_workers=6) as ex:
         peaks = ex.submit(build_peaks, force)
         probe = ex.submit(build_smem_probe, force)
+        cudnn = ex.submit(build_cudnn_probe, force)
         libs = list(ex.map(lambda v: build_variant(v, force, verbose), VARIANTS))
+        cudnn.result()                   # optional: absent where cuDNN is not installed
         return libs + [peaks.result(), probe.result()]
 
 

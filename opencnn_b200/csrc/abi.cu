@@ -130,6 +130,11 @@ cudaError_t device_state(DeviceState **out) {
 }
 
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+// What the output pointer must be aligned to: the tensor-core kernels store 32 bytes per lane
+// (st.global.v8.f32), the fp32 kernel at most 8.
+bool output_aligned(const void *p, int precision) {
+  return (reinterpret_cast<uintptr_t>(p) & (precision == OPENCNN_FP32 ? 15u : 31u)) == 0;
+}
 
 // What the batch and the channel count must be multiples of.  The two legacy entry points keep
 // the reference's rules (N % 32, C % 8).  The other entries accept a ragged last block of images
@@ -352,16 +357,12 @@ cudaError_t launch_wino_tc2(const float *input, const float *workspace, float *o
 // epilogue (two CTAs meet through L2), so it wins where a tile has many K-steps and the MMAs are
 // many: in TF32 from 64 K-steps per tile (C >= 512: 6-20 % ahead).  In BF16 the single-CTA kernel
 // is level or ahead everywhere since it issues its MMAs from two threads (C = 1024: within 1 %),
-// so BF16 never takes the pair.  OCB_TC_PAIR forces one of them (0 / 1) for experiments.
+// so BF16 never takes the pair.
 template <int DT>
 cudaError_t launch_tc(const float *input, const float *workspace, float *output, int N, int C, int H, int W, int K,
                       cudaStream_t stream) {
-#if defined(OCB_TC_PAIR)
-  const bool pair = OCB_TC_PAIR != 0;
-#else
   const int k_steps = (C + ocb::TcCfg<DT>::kKC - 1) / ocb::TcCfg<DT>::kKC;
   const bool pair = DT == ocb::kTcTf32 && k_steps >= 64 && N >= 64;
-#endif
   return pair ? launch_wino_tc2<DT>(input, workspace, output, N, C, H, W, K, stream)
               : launch_wino_tc<DT>(input, workspace, output, N, C, H, W, K, stream);
 }
@@ -371,6 +372,7 @@ cudaError_t forward(const float *input, const float *filter, float *output, floa
   if (!input || !filter || !output || !workspace) return cudaErrorInvalidValue;
   if (!aligned16(input) || !aligned16(filter) || !aligned16(output) || !aligned16(workspace)) return cudaErrorInvalidValue;
   if (precision != OPENCNN_FP32 && precision != OPENCNN_TF32 && precision != OPENCNN_BF16) return cudaErrorInvalidValue;
+  if (!output_aligned(output, precision)) return cudaErrorInvalidValue;
   cudaError_t e = check_shape(N, C, H, W, K, rule);
   if (e != cudaSuccess) return e;
   if (precision == OPENCNN_BF16) {
@@ -474,6 +476,7 @@ int opencnn_winograd_forward(const float *input, const float *workspace, float *
   if (!input || !workspace || !output) return (int)cudaErrorInvalidValue;
   if (!aligned16(input) || !aligned16(workspace) || !aligned16(output)) return (int)cudaErrorInvalidValue;
   if (precision != OPENCNN_FP32 && precision != OPENCNN_TF32 && precision != OPENCNN_BF16) return (int)cudaErrorInvalidValue;
+  if (!output_aligned(output, precision)) return (int)cudaErrorInvalidValue;
   cudaError_t e = check_shape(in_n, in_c, in_h, in_w, filt_k, shape_rule(precision));
   if (e != cudaSuccess) return (int)e;
   if (precision == OPENCNN_BF16)
@@ -571,6 +574,17 @@ int opencnn_host_plan_run_async(void *plan, const float *input_host, const float
   if (e == cudaSuccess)
     e = forward(hp->d_in, hp->d_filt, hp->d_out, hp->d_ws, hp->N, hp->C, hp->H, hp->W, hp->K, hp->precision, hp->stream,
                 shape_rule(hp->precision));
+  if (e == cudaSuccess) e = cudaMemcpyAsync(output_host, hp->d_out, out_b, cudaMemcpyDeviceToHost, hp->stream);
+  return (int)e;
+}
+
+int opencnn_host_plan_copy_async(void *plan, const float *input_host, const float *filter_host, float *output_host) {
+  HostPlan *hp = static_cast<HostPlan *>(plan);
+  if (!hp || !input_host || !filter_host || !output_host) return (int)cudaErrorInvalidValue;
+  const size_t in_b = (size_t)hp->N * hp->C * hp->H * hp->W * 4, f_b = (size_t)hp->C * 9 * hp->K * 4;
+  const size_t out_b = (size_t)hp->N * hp->K * hp->H * hp->W * 4;
+  cudaError_t e = cudaMemcpyAsync(hp->d_filt, filter_host, f_b, cudaMemcpyHostToDevice, hp->stream);
+  if (e == cudaSuccess) e = cudaMemcpyAsync(hp->d_in, input_host, in_b, cudaMemcpyHostToDevice, hp->stream);
   if (e == cudaSuccess) e = cudaMemcpyAsync(output_host, hp->d_out, out_b, cudaMemcpyDeviceToHost, hp->stream);
   return (int)e;
 }

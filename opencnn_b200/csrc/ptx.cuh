@@ -57,8 +57,12 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 }
 // Waits for a phase of an mbarrier, but never for ever: after `limit_ns` of wall time (or as
 // soon as another thread of the CTA has given up) it sets the CTA's `dead` word and the global
-// status word and returns false.  The caller carries on with whatever is in shared memory, so
-// the kernel still terminates; the host sees the failure in the status word.
+// status word and returns false.  What a caller does then depends on its role: a thread that
+// issues asynchronous work (TMA loads, tensor-core MMAs) stops issuing and waits, again with a
+// limit, for what it has in flight (mbar_wait_drain); every other thread carries on with
+// whatever is in shared memory - all its later waits return at once - so that block-wide and
+// group-wide barriers are still reached by everyone and the kernel terminates.  The host sees
+// the failure in the status word.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *dead, int *status,
                                           uint64_t limit_ns = 2000000000ull) {
   // (Polling with the non-suspending test_wait first was measured and is slower: the spinning
@@ -76,6 +80,18 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         return false;
       }
     }
+  }
+}
+
+// Bounded wait that ignores the CTA's `dead` word: used once a thread has given up, to let the
+// asynchronous operations it issued earlier (whose completion this barrier phase signals) finish
+// before the CTA exits or frees what they use.  Returns false if the limit ran out.
+__device__ __forceinline__ bool mbar_wait_drain(uint32_t bar, uint32_t parity, uint64_t limit_ns = 2000000000ull) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = global_timer_ns();
+  for (uint32_t spin = 1;; ++spin) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((spin & 63u) == 0u && global_timer_ns() - t0 > limit_ns) return false;
   }
 }
 

@@ -18,6 +18,16 @@ enum Op : int { kLds32 = 0, kLds64, kLds128, kSts32, kSts64, kSts128 };
 //  4 the reference's optSTS64 deposit pattern (src/store_and_transform_output_optSTS64.cuh:73-75, pitch 138 float2)
 //  5 this library's main-loop image-pair LDS.128 (4 distinct quads per half-warp, swapped in odd quarters)
 //  6 this library's main-loop filter LDS.128 (8 distinct quads per half-warp)
+//  7 the reference's "opt3" 64-bit pattern, used for both its optLDS64 read-back and its STS.64 probe: the 32
+//    lanes cover 256 contiguous bytes, but lanes 8-15 and 16-23 are swapped, so that lanes {0-7, 16-23} hold
+//    the first 128 bytes and {8-15, 24-31} the second (bench/smem/LDS/lds64_opt3.sass:13-27,
+//    bench/smem/STS/sts64_opt3.sass:14-29)
+//  8 the reference's two-way-conflict STS.64: 64-bit words 0, 2, .. 30 in lanes 0-15 and 32, 34, .. 62 in
+//    lanes 16-31 (bench/smem/STS/sts64_2bank_conflict.sass:13-22)
+//  9 the reference's same-address STS.64: word (lane % 8), i.e. every address four times
+//    (bench/smem/STS/sts64_broadcast.sass:13-27)
+// 10 the reference's half-active STS.128: lane * 16 bytes, only lanes with lane % 16 <= 8 take part
+//    (bench/smem/STS/sts128.sass:13-22, run at bench/smem/STS/main.cu:99-100)
 __device__ __forceinline__ uint32_t lane_offset(int pattern, int lane, int width) {
   switch (pattern) {
     case 0: return lane * width;
@@ -39,9 +49,18 @@ __device__ __forceinline__ uint32_t lane_offset(int pattern, int lane, int width
       const int q = lane >> 3, qp = q & 1, kg = (lane & 7) >> 1;
       return (uint32_t)((q * 64 + 8 * kg + 4 * qp) * 4);
     }
+    case 7: {
+      const int a = lane % 16;
+      return (uint32_t)((((lane / 16) * 8 + a) + (a >= 8 ? 8 : 0)) * 8);
+    }
+    case 8: return (uint32_t)((((lane * 2) % 32) + (lane / 16) * 32) * 8);
+    case 9: return (uint32_t)((lane % 8) * 8);
+    case 10: return lane * 16;
     default: return 0;
   }
 }
+// Pattern 10 runs with part of the warp switched off, like the reference's kernel (its inactive lanes exit).
+__device__ __forceinline__ bool lane_active(int pattern, int lane) { return pattern != 10 || (lane % 16) <= 8; }
 
 // clock read that the compiler may not move across the volatile loads and stores
 __device__ __forceinline__ long long clock_now() {
@@ -58,6 +77,7 @@ __global__ void __launch_bounds__(32, 1) smem_probe_kernel(long long *clocks, in
   constexpr int width = (OP == kLds32 || OP == kSts32) ? 4 : (OP == kLds64 || OP == kSts64) ? 8 : 16;
   const uint32_t addr = (uint32_t)__cvta_generic_to_shared(buf) + lane_offset(pattern, threadIdx.x, width);
   float a = 1.f, b = 2.f, c = 3.f, d = 4.f;
+  if (!lane_active(pattern, threadIdx.x)) return;
   const long long t0 = clock_now();
   for (int outer = 0; outer < 128; ++outer) {
 #pragma unroll
@@ -80,7 +100,7 @@ __global__ void __launch_bounds__(32, 1) smem_probe_kernel(long long *clocks, in
 // op: 0 LDS.32, 1 LDS.64, 2 LDS.128, 3 STS.32, 4 STS.64, 5 STS.128; pattern: see lane_offset.
 // Writes clocks per warp instruction.  Synchronous.  Returns a cudaError_t code.
 extern "C" int opencnn_smem_probe(int op, int pattern, double *clocks_per_instruction) {
-  if (op < 0 || op > 5 || pattern < 0 || pattern > 6 || !clocks_per_instruction) return (int)cudaErrorInvalidValue;
+  if (op < 0 || op > 5 || pattern < 0 || pattern > 10 || !clocks_per_instruction) return (int)cudaErrorInvalidValue;
   long long *d_clk = nullptr;
   float *d_sink = nullptr;
   cudaError_t e = cudaMalloc(&d_clk, sizeof(long long));

@@ -30,21 +30,6 @@
 #pragma once
 #include "ptx.cuh"
 
-// Timing experiments only (never defined in shipped builds): bit 0 skips the input transform,
-// bit 1 skips the TMA loads, bit 2 skips the epilogue.  Results are then wrong by construction.
-#ifndef OCB_ABLATE
-#define OCB_ABLATE 0
-#endif
-#ifndef OCB_LAG
-#define OCB_LAG 0
-#endif
-#ifndef OCB_PAIR_TRANSFORM
-#define OCB_PAIR_TRANSFORM 0
-#endif
-#ifndef OCB_FMA_ORDER
-#define OCB_FMA_ORDER 0
-#endif
-
 namespace ocb {
 
 enum Variant : int { kBase = 0, kOptSts64 = 1, kOptSts64Cmp = 2, kOptLds64 = 3 };
@@ -315,28 +300,6 @@ __device__ __forceinline__ void transform_patch(float *vstage, int patch) {
     R[(4 * i + 3) * kBN] = __fsub_rn(b[4 * i + 1], b[4 * i + 3]);
   }
 }
-__device__ __forceinline__ void transform_patch_pair(float *vstage, int t) {
-  uint64_t *R = reinterpret_cast<uint64_t *>(vstage + ((t >> 4) * 16) * kBN + 2 * (t & 15));
-  constexpr int P = kBN / 2;   // row pitch in pairs
-  uint64_t d[16], b[16];
-#pragma unroll
-  for (int q = 0; q < 16; ++q) d[q] = R[q * P];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    b[j] = sub2(d[j], d[8 + j]);
-    b[4 + j] = add2(d[4 + j], d[8 + j]);
-    b[8 + j] = sub2(d[8 + j], d[4 + j]);
-    b[12 + j] = sub2(d[4 + j], d[12 + j]);
-  }
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    R[(4 * i + 0) * P] = sub2(b[4 * i + 0], b[4 * i + 2]);
-    R[(4 * i + 1) * P] = add2(b[4 * i + 1], b[4 * i + 2]);
-    R[(4 * i + 2) * P] = sub2(b[4 * i + 2], b[4 * i + 1]);
-    R[(4 * i + 3) * P] = sub2(b[4 * i + 1], b[4 * i + 3]);
-  }
-}
-
 // Operands of one channel for one lane: 16 images as 8 pairs, 8 filters.
 struct Frag {
   ulonglong2 v[4];
@@ -363,17 +326,10 @@ __device__ __forceinline__ void fma_frag(uint64_t (&acc)[8][8], const Frag &f) {
   uint64_t dup[8];
 #pragma unroll
   for (int kk = 0; kk < 8; ++kk) dup[kk] = pack2(uu[kk], uu[kk]);
-#if OCB_FMA_ORDER == 1
-#pragma unroll
-  for (int qq = 0; qq < 8; ++qq)
-#pragma unroll
-    for (int kk = 0; kk < 8; ++kk) ffma2(acc[kk][qq], vv[qq], dup[kk]);
-#else
 #pragma unroll
   for (int kk = 0; kk < 8; ++kk)
 #pragma unroll
     for (int qq = 0; qq < 8; ++qq) ffma2(acc[kk][qq], vv[qq], dup[kk]);
-#endif
 }
 
 template <int V, bool RAGGED>
@@ -412,26 +368,29 @@ wino_fp32_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constan
       if (lane == 0) {
         tma_prefetch_descriptor(&tm_in);
         tma_prefetch_descriptor(&tm_u);
-        int seq = 0, ci = 0, groups_unused;
+        int seq = 0, ci = 0, groups_unused, issued = 0;
         TileCoord tc = decode_tile(p, item_tile(p, (int)blockIdx.x, groups_unused));
         for (int g = 0; g < total_chunks; ++g) {
           const int s = g % S;
-          if (g >= S) mbar_wait(smem_u32(bar_empty + s), ((g / S) - 1) & 1, dead, p.status);
+          // A wait that gave up: stop issuing - the stage may still be in use.
+          if (g >= S && !mbar_wait(smem_u32(bar_empty + s), ((g / S) - 1) & 1, dead, p.status)) break;
           const uint32_t bar = smem_u32(bar_full + s);
           const uint32_t dst = smem_u32(stages + s * kStageFloats);
-          if (OCB_ABLATE & 2) {
-            mbar_arrive(bar);
-          } else {
-            mbar_arrive_expect_tx(bar, kStageBytes);
-            tma_load_4d(dst, &tm_in, bar, tc.nb * kBN, 2 * tc.tx - 1, 2 * tc.ty - 1, ci * kBC);
-            tma_load_3d(dst + kVStageFloats * 4u, &tm_u, bar, tc.kb * kBK, 0, ci * kBC);
-          }
+          mbar_arrive_expect_tx(bar, kStageBytes);
+          tma_load_4d(dst, &tm_in, bar, tc.nb * kBN, 2 * tc.tx - 1, 2 * tc.ty - 1, ci * kBC);
+          tma_load_3d(dst + kVStageFloats * 4u, &tm_u, bar, tc.kb * kBK, 0, ci * kBC);
+          issued = g + 1;
           if (++ci == cpt) {
             ci = 0;
             ++seq;
             if (seq < my_tiles) tc = decode_tile(p, item_tile(p, (int)blockIdx.x + seq * (int)gridDim.x, groups_unused));
           }
         }
+        // The CTA must not exit with bulk copies in flight.  After a complete run the last loads
+        // were consumed long ago and these waits return at once; after a give-up they let what
+        // was issued land (with a limit of their own).
+        for (int g = issued > S ? issued - S : 0; g < issued; ++g)
+          mbar_wait_drain(smem_u32(bar_full + g % S), (g / S) & 1);
       }
     } else {
       // ---- transform warps: raw patch -> V, in place, as soon as a stage has landed ----
@@ -440,13 +399,7 @@ wino_fp32_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constan
         const int s = g % S;
         mbar_wait(smem_u32(bar_full + s), (g / S) & 1, dead, p.status);
         float *vst = stages + s * kStageFloats;
-        if (!(OCB_ABLATE & 1)) {
-#if OCB_PAIR_TRANSFORM
-          for (int pair = t; pair < kBC * kBN / 2; pair += kTransformThreads) transform_patch_pair(vst, pair);
-#else
-          for (int patch = t; patch < kBC * kBN; patch += kTransformThreads) transform_patch(vst, patch);
-#endif
-        }
+        for (int patch = t; patch < kBC * kBN; patch += kTransformThreads) transform_patch(vst, patch);
         fence_proxy_async_smem();     // these generic writes precede the TMA that refills the stage
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(bar_ready + s));
@@ -469,12 +422,6 @@ wino_fp32_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constan
   for (int a = 0; a < 8; ++a)
 #pragma unroll
     for (int b = 0; b < 8; ++b) acc[a][b] = 0ull;
-
-  // Experiment hook: start group 1 kLag chunks behind group 0 so that the two epilogues do not
-  // coincide.  With a ring of 3-4 stages the leading group then starves for loads, and no lag
-  // measured fastest, so the shipped value is 0.
-  constexpr int kLag = OCB_LAG;
-  if (kLag > 0 && role.gi == 1 && total_chunks > kLag) mbar_wait(smem_u32(bar_ready + kLag), 0, dead, p.status);
 
   // Two operand buffers used alternately: channel c computes from frag[c & 1] while frag[(c + 1) & 1]
   // is being loaded.  With the channel loop unrolled the indices are constants, so no register
@@ -522,16 +469,7 @@ wino_fp32_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constan
         }
       }
       const TileCoord tc = decode_tile(p, tile);
-      if (!(OCB_ABLATE & 4)) {
-        epilogue<V, RAGGED>(acc, my_stg, p, tc, role);
-      } else {                                                    // keeps the accumulators alive
-        uint64_t x = 0;
-#pragma unroll
-        for (int a = 0; a < 8; ++a)
-#pragma unroll
-          for (int b = 0; b < 8; ++b) x ^= acc[a][b];
-        if (x == 0x123456789ull) p.y[tid] = 1.f;
-      }
+      epilogue<V, RAGGED>(acc, my_stg, p, tc, role);
 #pragma unroll
       for (int a = 0; a < 8; ++a)
 #pragma unroll

@@ -30,12 +30,6 @@
 #include "ptx.cuh"
 #include "wino_fp32.cuh"   // WinoParams, TileCoord, output_transform, add2/sub2
 
-// Timing experiments only (never defined in shipped builds): bit 0 skips the U loads, bit 1 the
-// raw-input loads, bit 2 the input transform, bit 3 the MMAs, bit 4 the epilogue's loads/stores.
-#ifndef OCB_TC_ABLATE
-#define OCB_TC_ABLATE 0
-#endif
-
 namespace ocb {
 
 enum TcType : int { kTcBf16 = 0, kTcTf32 = 1 };
@@ -265,6 +259,7 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
   uint64_t *acc_full = u_full + 6, *acc_empty = u_full + 7;
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(u_full + 8);
   volatile int *dead = reinterpret_cast<volatile int *>(u_full + 9);
+  uint64_t *mma_done = u_full + 10;                    // one per MMA-issuing thread: "all my MMAs have completed"
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int my_tiles = (p.total_tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x;
@@ -283,6 +278,7 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
     }
     mbar_init(smem_u32(acc_full), Cfg::kIssuers);
     mbar_init(smem_u32(acc_empty), kTcEpilogueWarps);
+    for (int i = 0; i < Cfg::kIssuers; ++i) mbar_init(smem_u32(mma_done + i), 1);
     mbar_fence_init();
   }
   if (warp == kTcMmaWarp) tmem_alloc_512(smem_u32(tmem_slot));
@@ -299,39 +295,40 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
     const bool loads_u = warp != 0;
     if (lane == 0) {
       tma_prefetch_descriptor(loads_u ? &tm_u : &tm_in);
-      int seq = 0, ci = 0;
+      int seq = 0, ci = 0, issued = 0;
       TileCoord tc = decode_tile(p, (int)blockIdx.x);
       for (int g = 0; g < total_chunks; ++g) {
         const int s = g % kTcStages;
         const uint32_t use = g / kTcStages;
+        // A wait that gave up: stop issuing - the stage may still be in use.
         if (!loads_u) {
           const int sr = g % SR;
           const uint32_t use_r = g / SR;
-          if (use_r > 0) mbar_wait(smem_u32(raw_empty + sr), (use_r - 1) & 1, dead, p.status);
-          if (OCB_TC_ABLATE & 2) {
-            mbar_arrive(smem_u32(raw_full + sr));
-          } else {
-            mbar_arrive_expect_tx(smem_u32(raw_full + sr), Cfg::kRawBytes);
-            tma_load_4d(smem_u32(raw_s + sr * Cfg::kRawBytes), &tm_in, smem_u32(raw_full + sr), tc.nb * kTcN,
-                        2 * tc.tx - 1, 2 * tc.ty - 1, ci * KC);
-          }
+          if (use_r > 0 && !mbar_wait(smem_u32(raw_empty + sr), (use_r - 1) & 1, dead, p.status)) break;
+          mbar_arrive_expect_tx(smem_u32(raw_full + sr), Cfg::kRawBytes);
+          tma_load_4d(smem_u32(raw_s + sr * Cfg::kRawBytes), &tm_in, smem_u32(raw_full + sr), tc.nb * kTcN,
+                      2 * tc.tx - 1, 2 * tc.ty - 1, ci * KC);
         } else {
-          if (use > 0) mbar_wait(smem_u32(uv_empty + s), (use - 1) & 1, dead, p.status);
-          if (OCB_TC_ABLATE & 1) {
-            mbar_arrive(smem_u32(u_full + s));
-          } else {
-            mbar_arrive_expect_tx(smem_u32(u_full + s), Cfg::kUBytes);
-            // U viewed as {filters within a 128-byte row, channel, 128-byte row of the filter axis, position}
-            tma_load_4d(smem_u32(u_s + s * Cfg::kUBytes), &tm_u, smem_u32(u_full + s), 0, ci * KC,
-                        tc.kb * (DT == kTcBf16 ? 2 : 4), 0);
-          }
+          if (use > 0 && !mbar_wait(smem_u32(uv_empty + s), (use - 1) & 1, dead, p.status)) break;
+          mbar_arrive_expect_tx(smem_u32(u_full + s), Cfg::kUBytes);
+          // U viewed as {filters within a 128-byte row, channel, 128-byte row of the filter axis, position}
+          tma_load_4d(smem_u32(u_s + s * Cfg::kUBytes), &tm_u, smem_u32(u_full + s), 0, ci * KC,
+                      tc.kb * (DT == kTcBf16 ? 2 : 4), 0);
         }
+        issued = g + 1;
         if (++ci == cpt) {
           ci = 0;
           ++seq;
           if (seq < my_tiles) tc = decode_tile(p, (int)blockIdx.x + seq * (int)gridDim.x);
         }
       }
+      // No exit with bulk copies in flight: wait (with a limit of its own) for the last loads of
+      // every stage.  After a complete run these phases are long over.  u_full also counts the
+      // transform warps' arrivals; after a give-up those may be missing, and then the limit ends
+      // the wait.
+      const int ring = loads_u ? kTcStages : SR;
+      for (int g = issued > ring ? issued - ring : 0; g < issued; ++g)
+        mbar_wait_drain(smem_u32((loads_u ? u_full : raw_full) + g % ring), (g / ring) & 1);
     }
   } else if (warp <= kTcTransformWarps) {
     // ===================================== input transform =====================================
@@ -343,8 +340,7 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
       if (use > 0) mbar_wait(smem_u32(uv_empty + s), (use - 1) & 1, dead, p.status);   // V stage free again
       const float *raw = reinterpret_cast<const float *>(raw_s + sr * Cfg::kRawBytes);
       uint8_t *vst = v_s + s * kTcVBytes;
-      if (OCB_TC_ABLATE & 4) {
-      } else if (DT == kTcBf16) {
+      if (DT == kTcBf16) {
         transform_to_v_bf16_x2(raw, vst, t >> 4, t & 15);          // 16 channels x 16 image pairs, two items per thread
       } else {
         transform_to_v_tf32_pair(raw, vst, t >> 4, t & 15);        // 8 channels x 16 image pairs = 128 threads
@@ -384,13 +380,14 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
       for (int g = 0; g < total_chunks; ++g) {
         const int s = g % kTcStages;
         const uint32_t use = g / kTcStages;
-        mbar_wait(smem_u32(u_full + s), use & 1, dead, p.status);      // U landed and V written
-        if (ci == 0 && seq > 0) mbar_wait(smem_u32(acc_empty), (seq - 1) & 1, dead, p.status);   // TMEM drained
+        // A wait that gave up: stop issuing (the operands or the accumulators are not ready).
+        if (!mbar_wait(smem_u32(u_full + s), use & 1, dead, p.status)) break;      // U landed and V written
+        if (ci == 0 && seq > 0 && !mbar_wait(smem_u32(acc_empty), (seq - 1) & 1, dead, p.status)) break;   // TMEM drained
         tc_fence_after();
         const uint64_t ad = ((dup || HU) ? a_desc0_dup : a_desc0) + (uint64_t)(s * (Cfg::kUBytes >> 4)), bd = b_desc0 + (uint64_t)(s * (kTcVBytes >> 4));
         const uint32_t accumulate = ci > 0 ? 1u : 0u;
 #pragma unroll
-        for (int xo = 0; xo < ((OCB_TC_ABLATE & 8) ? 0 : kPer); ++xo) {
+        for (int xo = 0; xo < kPer; ++xo) {
           const int xi = x0 + xo;
           tc_mma<DT>(tmem_base + xi * kTcN, ad + (uint64_t)(xi * (Cfg::kUPosBytes >> 4)), bd + (uint64_t)(xi * (1024 >> 4)), idesc, accumulate);
         }
@@ -402,6 +399,11 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
           if (seq < my_tiles) dup = tile_repeats_filters<DT>(p, decode_tile(p, (int)blockIdx.x + seq * (int)gridDim.x));
         }
       }
+      // Tensor memory is freed at the end of the kernel: every MMA this thread issued must have
+      // completed by then, also after a give-up (then nobody waited for acc_full).
+      const int me = warp == kTcMmaWarp ? 0 : warp - kTcMmaWarpB + 1;
+      tc_commit(smem_u32(mma_done + me));
+      mbar_wait_drain(smem_u32(mma_done + me), 0);
     }
   } else {
     // ===================================== epilogue ============================================
@@ -428,7 +430,7 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
       // Warps whose 32 filters all lie beyond K (K = 64 layers) have nothing to read or store.
       const bool warp_valid = (tc.kb * kTcM + fq * 32) < p.K;
       // this warp's share of the 32 images: image quads jbase .. jbase + iters - 1
-      const int iters = (OCB_TC_ABLATE & 16) ? 0 : (dup ? 2 : 4);
+      const int iters = dup ? 2 : 4;
       const int jbase = dup ? 2 * (2 * (quarter >> 1) + sub) : 4 * sub;
       bool released = false;
 #pragma unroll 1
@@ -473,7 +475,7 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
           }
         }
       }
-      if (!released) {                       // warps without valid filters, or ablated epilogue
+      if (!released) {                       // warps without valid filters
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(acc_empty));

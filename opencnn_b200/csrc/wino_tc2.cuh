@@ -57,6 +57,7 @@ __device__ __forceinline__ void mbar_arrive_remote(uint32_t local_bar, uint32_t 
       "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n\t}"
       ::"r"(local_bar), "r"(rank) : "memory");
 }
+__device__ __forceinline__ void fence_acq_rel_cluster() { asm volatile("fence.acq_rel.cluster;" ::: "memory"); }
 __device__ __forceinline__ void red_global_add_v4(float *p, const float (&a)[4]) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a[0]), "f"(a[1]), "f"(a[2]), "f"(a[3]) : "memory");
 }
@@ -93,7 +94,8 @@ __device__ __forceinline__ void p2_finish_bf16(const uint64_t (&d)[12], uint8_t 
     }
   }
 }
-// Two items (channels c and c + 8 of image pair np) at once, loads first (see the TF32 version).
+// Two items (channels c and c + 8 of image pair np) at once: all loads are issued before any
+// arithmetic, so the two shared-memory round trips overlap.
 template <int RANK>
 __device__ __forceinline__ void p2_transform_bf16_x2(const float *__restrict__ raw, uint8_t *__restrict__ vst, int c, int np) {
   const uint64_t *R0 = reinterpret_cast<const uint64_t *>(raw + (c * 12) * kP2N + 2 * np), *R1 = R0 + 8 * 12 * (kP2N / 2);
@@ -104,35 +106,8 @@ __device__ __forceinline__ void p2_transform_bf16_x2(const float *__restrict__ r
   p2_finish_bf16<RANK>(d0, vst, c, np);
   p2_finish_bf16<RANK>(d1, vst, c + 8, np);
 }
-// TF32: item = (channel c, image n of 64); V tile of a position is [2 image blocks][8 c][32 n] fp32,
-// rows of 128 bytes, 128-byte swizzle with 32-byte atoms.
-template <int RANK>
-__device__ __forceinline__ void p2_finish_tf32(const float (&d)[12], uint8_t *__restrict__ vst, int c, int n) {
-  float b[8];
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    if (RANK == 0) {
-      b[j] = __fsub_rn(d[j], d[8 + j]);
-      b[4 + j] = __fadd_rn(d[4 + j], d[8 + j]);
-    } else {
-      b[j] = __fsub_rn(d[4 + j], d[j]);
-      b[4 + j] = __fsub_rn(d[j], d[8 + j]);
-    }
-  }
-  const int nl = n & 31;
-  uint8_t *dst = vst + (n >> 5) * 1024 + c * 128 + ((((nl >> 3) ^ c) & 3) << 5) + ((nl & 7) << 2);
-#pragma unroll
-  for (int ii = 0; ii < 2; ++ii) {
-    float o[4];
-    o[0] = __fsub_rn(b[4 * ii + 0], b[4 * ii + 2]);
-    o[1] = __fadd_rn(b[4 * ii + 1], b[4 * ii + 2]);
-    o[2] = __fsub_rn(b[4 * ii + 2], b[4 * ii + 1]);
-    o[3] = __fsub_rn(b[4 * ii + 1], b[4 * ii + 3]);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) *reinterpret_cast<float *>(dst + (4 * ii + j) * 2048) = round_tf32_rne(o[j]);
-  }
-}
-// Packed form: one item = (channel c, image pair np of 32); the two images of a pair are adjacent
+// TF32: one item = (channel c, image pair np of 32); V tile of a position is [2 image blocks][8 c][32 n]
+// fp32, rows of 128 bytes, 128-byte swizzle with 32-byte atoms; the two images of a pair are adjacent
 // in a V row, so each result is one 8-byte store.
 template <int RANK>
 __device__ __forceinline__ void p2_transform_tf32_pair(const float *__restrict__ raw, uint8_t *__restrict__ vst, int c, int np) {
@@ -168,18 +143,6 @@ __device__ __forceinline__ void p2_transform_tf32_pair(const float *__restrict__
     }
   }
 }
-// Two items (channels c and c + 4 of image n) at once: all 24 loads are issued before any
-// arithmetic, so the two shared-memory round trips overlap.
-template <int RANK>
-__device__ __forceinline__ void p2_transform_tf32_x2(const float *__restrict__ raw, uint8_t *__restrict__ vst, int c, int n) {
-  const float *R0 = raw + (c * 12) * kP2N + n, *R1 = R0 + 4 * 12 * kP2N;
-  float d0[12], d1[12];
-#pragma unroll
-  for (int q = 0; q < 12; ++q) { d0[q] = R0[q * kP2N]; d1[q] = R1[q * kP2N]; }
-  p2_finish_tf32<RANK>(d0, vst, c, n);
-  p2_finish_tf32<RANK>(d1, vst, c + 4, n);
-}
-
 // Partial output transform of one (filter, image) from the 8 positions of rows 2*RANK, 2*RANK+1:
 // m[0..3] = row 2*RANK, m[4..7] = row 2*RANK+1.  The sum of the two ranks' results is A^T M A.
 template <int RANK>
@@ -221,6 +184,7 @@ __device__ __forceinline__ void p2_body(const CUtensorMap &tm_in, const CUtensor
   uint64_t *acc_full = bars + 5 * S, *acc_empty = acc_full + 1, *peer_ready = acc_full + 2;   // peer_ready[2], used alternately
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 4);
   volatile int *dead = reinterpret_cast<volatile int *>(acc_full + 5);
+  uint64_t *mma_done = acc_full + 6;                   // one per MMA-issuing thread: "all my MMAs have completed"
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_clusters = (int)gridDim.x / 2, cid = (int)blockIdx.x / 2;
@@ -242,6 +206,8 @@ __device__ __forceinline__ void p2_body(const CUtensorMap &tm_in, const CUtensor
     mbar_init(smem_u32(peer_ready + 1), kP2EpilogueWarps);
     mbar_init(smem_u32(acc_full), 2);
     mbar_init(smem_u32(acc_empty), kP2EpilogueWarps);
+    mbar_init(smem_u32(mma_done + 0), 1);
+    mbar_init(smem_u32(mma_done + 1), 1);
     mbar_fence_init();
   }
   if (warp == kP2MmaWarp) tmem_alloc_512(smem_u32(tmem_slot));
@@ -256,28 +222,33 @@ __device__ __forceinline__ void p2_body(const CUtensorMap &tm_in, const CUtensor
     const bool loads_u = warp != 0;
     if (lane == 0) {
       tma_prefetch_descriptor(loads_u ? &tm_u : &tm_in);
-      int seq = 0, ci = 0;
+      int seq = 0, ci = 0, issued = 0;
       P2Tile tc = p2_decode(p, cid, n_pairs);
       for (int g = 0; g < total_chunks; ++g) {
         const int s = g % S;
         const uint32_t use = g / S;
+        // A wait that gave up: stop issuing - the stage may still be in use.
         if (!loads_u) {
-          if (use > 0) mbar_wait(smem_u32(raw_empty + s), (use - 1) & 1, dead, p.status);
+          if (use > 0 && !mbar_wait(smem_u32(raw_empty + s), (use - 1) & 1, dead, p.status)) break;
           mbar_arrive_expect_tx(smem_u32(raw_full + s), Cfg::kRawBytes);
           tma_load_4d(smem_u32(raw_s + s * Cfg::kRawBytes), &tm_in, smem_u32(raw_full + s), tc.np * kP2N, 2 * tc.tx - 1,
                       2 * tc.ty - 1 + RANK, ci * KC);           // patch rows RANK .. RANK+2
         } else {
-          if (use > 0) mbar_wait(smem_u32(uv_empty + s), (use - 1) & 1, dead, p.status);
+          if (use > 0 && !mbar_wait(smem_u32(uv_empty + s), (use - 1) & 1, dead, p.status)) break;
           mbar_arrive_expect_tx(smem_u32(u_full + s), kP2UBytes);
           tma_load_4d(smem_u32(u_s + s * kP2UBytes), &tm_u, smem_u32(u_full + s), 0, ci * KC,
                       tc.kb * (DT == kTcBf16 ? 2 : 4), 8 * RANK);
         }
+        issued = g + 1;
         if (++ci == cpt) {
           ci = 0;
           ++seq;
           if (seq < my_tiles) tc = p2_decode(p, cid + seq * n_clusters, n_pairs);
         }
       }
+      // No exit with bulk copies in flight (see wino_tc.cuh).
+      for (int g = issued > S ? issued - S : 0; g < issued; ++g)
+        mbar_wait_drain(smem_u32((loads_u ? u_full : raw_full) + g % S), (g / S) & 1);
     }
   } else if (warp >= 1 && warp <= kP2TransformWarps) {
     // ===================================== input transform =====================================
@@ -316,9 +287,10 @@ __device__ __forceinline__ void p2_body(const CUtensorMap &tm_in, const CUtensor
       for (int g = 0; g < total_chunks; ++g) {
         const int s = g % S;
         const uint32_t use = g / S;
-        mbar_wait(smem_u32(u_full + s), use & 1, dead, p.status);
-        mbar_wait(smem_u32(v_ready + s), use & 1, dead, p.status);
-        if (ci == 0 && seq > 0) mbar_wait(smem_u32(acc_empty), (seq - 1) & 1, dead, p.status);   // TMEM drained
+        // A wait that gave up: stop issuing.
+        if (!mbar_wait(smem_u32(u_full + s), use & 1, dead, p.status)) break;
+        if (!mbar_wait(smem_u32(v_ready + s), use & 1, dead, p.status)) break;
+        if (ci == 0 && seq > 0 && !mbar_wait(smem_u32(acc_empty), (seq - 1) & 1, dead, p.status)) break;   // TMEM drained
         tc_fence_after();
         const uint64_t ad = a_desc0 + (uint64_t)(s * (kP2UBytes >> 4)), bd = b_desc0 + (uint64_t)(s * (kP2VBytes >> 4));
         const uint32_t accumulate = ci > 0 ? 1u : 0u;
@@ -334,6 +306,10 @@ __device__ __forceinline__ void p2_body(const CUtensorMap &tm_in, const CUtensor
           ++seq;
         }
       }
+      // every MMA this thread issued must have completed before tensor memory is freed
+      const int me = warp == kP2MmaWarp ? 0 : 1;
+      tc_commit(smem_u32(mma_done + me));
+      mbar_wait_drain(smem_u32(mma_done + me), 0);
     }
   } else {
     // ===================================== epilogue ============================================
@@ -360,6 +336,7 @@ __device__ __forceinline__ void p2_body(const CUtensorMap &tm_in, const CUtensor
         if (phase == 1) {
           // the peer has stored its partial results for this block (its phase 0 of the same tile)
           mbar_wait(smem_u32(peer_ready + (seq & 1)), (seq >> 1) & 1, dead, p.status);
+          fence_acq_rel_cluster();       // pairs with the peer's release at cluster scope: its stores are visible
         }
         if (warp_valid && block_valid) {
           float *ybase = p.y + (size_t)k * plane + ((size_t)oh0 * p.W + ow0) * p.N + (size_t)(2 * tc.np + ib) * 32 + 16 * sub;

@@ -180,3 +180,17 @@ def ref_libs():
         if os.path.exists(p):
             out[v] = RefLib(p)
     return out
+
+
+def wait_probe_lib_path():
+    """Builds (if stale) the test-only bounded-wait probe, tests/wait_probe.cu."""
+    here = os.path.dirname(os.path.abspath(__file__))
+    src = os.path.join(here, "wait_probe.cu")
+    out = os.path.join(here, "_build", "libwait_probe.so")
+    deps = [src, os.path.join(ROOT, "opencnn_b200", "csrc", "ptx.cuh")]
+    if not os.path.exists(out) or any(os.path.getmtime(d) > os.path.getmtime(out) for d in deps):
+        from opencnn_b200 import build
+        os.makedirs(os.path.dirname(out), exist_ok=True)
+        subprocess.run([build.nvcc(), *build.ARCH, "-O3", "-lineinfo", "-std=c++17", "-Xcompiler", "-fPIC", "-shared",
+                        "-o", out, src], check=True, capture_output=True)
+    return out

@@ -72,3 +72,16 @@ def test_argument_errors_are_reported(libs, variant):
 def test_unknown_variant_rejected():
     with pytest.raises(ValueError):
         _lib.load("OPTSTS32")
+
+
+def test_tensor_core_output_must_be_32_byte_aligned(libs):
+    """The TF32 / BF16 kernels store 32 bytes per thread: a 16-byte-aligned output that is not 32-byte aligned
+    is refused before anything is launched (no GPU needed); fp32 accepts it."""
+    lib = libs["OPTSTS64"]
+    inval = api.cudaErrorInvalidValue
+    N, C, H, W, K = 32, 8, 8, 8, 64
+    for prec in (api.PRECISIONS["tf32"], api.PRECISIONS["bf16"]):
+        assert lib.opencnn_convolutionForward_stream(0x1000, 0x1000, 0x1010, 0x1000, N, C, H, W, K, prec, None) == inval
+        assert lib.opencnn_winograd_forward(0x1000, 0x1000, 0x1010, N, C, H, W, K, prec, None) == inval
+    # 8-byte-aligned pointers are refused everywhere
+    assert lib.opencnn_convolutionForward_stream(0x1000, 0x1000, 0x1008, 0x1000, N, C, H, W, K, 0, None) == inval

@@ -4,7 +4,8 @@ Two checks per case: (1) against the CPU model of exactly that computation (fp32
 operands rounded once, exact contraction) with a tight tolerance, which catches layout and
 indexing errors; (2) against the fp64 direct convolution with the tolerance the arithmetic
 allows, which is the accuracy claim of the path.  Inputs and filters are themselves rounded to
-the operand type first, as BASELINE's tensor-core configuration prescribes."""
+the operand type first (the tensor-core benchmark configuration prescribes operands rounded once
+from the seeded fp32 tensors)."""
 import numpy as np
 import pytest
 
@@ -105,3 +106,36 @@ def test_tensor_core_results_are_repeatable(libs, precision):
             torch.cuda.synchronize()
             assert torch.equal(first, again)
     assert api.last_device_status() == 0
+
+
+# The benchmark shapes at full size (the N=128 layer sweep and the two wide stress layers): error of both
+# operand types against 10^5 sampled fp64 outputs, relative to rms(truth).  The N=64 C=K=1024 layer takes the
+# CTA-pair kernel in TF32.
+FULL = [(128, 64, 64, 56), (128, 128, 128, 28), (128, 256, 256, 14), (128, 512, 512, 7), (64, 1024, 1024, 14),
+        (256, 32, 64, 112)]
+
+
+@pytest.mark.parametrize("precision", ["tf32", "bf16"])
+@pytest.mark.parametrize("shape", FULL)
+def test_tensor_core_error_at_benchmark_sizes(oracle, libs, precision, shape):
+    N, C, K, HW = shape
+    rnd = oracle.round_tf32 if precision == "tf32" else oracle.round_bf16
+    x = rnd(oracle.input_chwn(N, C, HW, HW)).reshape(C, HW, HW, N)
+    g = rnd(oracle.filter_crsk(C, K)).reshape(C, 3, 3, K)
+    dx, dg = torch.from_numpy(x).cuda(), torch.from_numpy(g).cuda()
+    dy = torch.full((K, HW, HW, N), float("nan"), device="cuda")
+    dws = torch.empty((C, 4, 4, K), device="cuda")
+    assert api.conv3x3(dx, dg, dy, dws, N, C, HW, HW, K, precision=precision) == 0
+    assert api.last_device_status() == 0
+    assert bool(torch.isfinite(dy).all().item()), "an output was not written"
+    idx = np.random.default_rng(11).integers(0, dy.numel(), 100000)
+    truth = oracle.direct_f64_sampled(x, g, idx)
+    got = dy.view(-1)[torch.from_numpy(idx).cuda()].cpu().numpy()
+    trms = float(np.sqrt(np.mean(truth ** 2)))
+    worst = float(np.abs(got - truth).max())
+    assert worst <= TRUTH_REL[precision] * trms, f"vs fp64: {worst / trms:.3e} of rms"
+    # a second run gives the same bits
+    dy2 = torch.empty_like(dy)
+    assert api.conv3x3(dx, dg, dy2, dws, N, C, HW, HW, K, precision=precision) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(dy, dy2)
