@@ -367,6 +367,10 @@ def main():
     flops_step = sum(direct_flops(*L) for L in LAYERS) * world
     value = flops_step / (ms_per_step * 1e-3) * 1e-12
 
+    # ---- per-kernel durations of the headline layers, taken right after the headline loop (the peak
+    # probes below load the chip far more heavily, and kernels timed just after them run slower) ------
+    headline_split = time_split(layers, args.variant, args.precision, reps=30, skip=5) if ours else None
+
     # ---- peaks ---------------------------------------------------------------------------------
     peaks = {}
     if ours:
@@ -415,10 +419,10 @@ def main():
             peaks.update(tf32_tflops=2.0 * 8192 ** 3 / (best * 1e-3) * 1e-12,
                          tf32_source="measured live: torch.matmul 8192^3 with TF32 operands (cuBLAS), best of 10 (burst)")
 
-    # ---- per-kernel durations of the headline layers (dominant kernel -> roofline) ---------------
+    # ---- dominant kernel -> roofline ------------------------------------------------------------
     per_layer, roof = [], None
     if ours:
-        split = time_split(layers, args.variant, args.precision, reps=30, skip=5)
+        split = headline_split
         tot_gemm = tot_ms = 0.0
         for L, (fx, fu) in zip(layers, split):
             shp = shape_of(L)

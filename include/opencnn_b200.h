@@ -75,6 +75,21 @@ int opencnn_filter_transform_p(const float *filter, float *workspace, int in_c, 
 int opencnn_winograd_forward(const float *input, const float *workspace, float *output, int in_n, int in_c,
                              int in_h, int in_w, int filt_k, int precision, opencnn_stream_t stream);
 
+/* The tensor-core fused kernel with the kernel chosen by the caller instead of by the library's own
+ * rule (precision must be OPENCNN_TF32 or OPENCNN_BF16; the workspace as written by
+ * opencnn_filter_transform_p for that precision).  All of them compute the same operator; they
+ * differ in how a tile is spread over SMs.  The reference has no counterpart (no tensor-core path). */
+enum opencnn_tc_kernel {
+  OPENCNN_TC_AUTO = 0,          /* what opencnn_winograd_forward would take */
+  OPENCNN_TC_SINGLE_CTA = 1,    /* one CTA per tile of 128 filters x 32 images, all 16 Winograd positions */
+  OPENCNN_TC_PAIR_LOCAL = 2,    /* CTA pair per 128 x 64 tile, positions split 8 / 8, each CTA transforms all 64 images */
+  OPENCNN_TC_PAIR_EXCHANGE = 3  /* CTA pair per 128 x 64 tile, each CTA transforms its 32 images and the halves are
+                                   exchanged through distributed shared memory */
+};
+int opencnn_winograd_forward_kernel(const float *input, const float *workspace, float *output, int in_n,
+                                    int in_c, int in_h, int in_w, int filt_k, int precision, int kernel,
+                                    opencnn_stream_t stream);
+
 /* Layout adapters for callers that hold cuDNN-style tensors.  They replace data_cpy
  * (src/openCNN_winograd.cu:147-153, launched :229-235), which scatters NCHW -> CHWN and
  * KCRS -> CRSK one element per thread, and the index arithmetic with which the reference compares

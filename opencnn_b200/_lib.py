@@ -23,6 +23,7 @@ SIGNATURES = {
     "opencnn_filter_transform": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "opencnn_filter_transform_p": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "opencnn_winograd_forward": (c_int, [c_void_p] * 3 + [c_int] * 6 + [c_void_p]),
+    "opencnn_winograd_forward_kernel": (c_int, [c_void_p] * 3 + [c_int] * 7 + [c_void_p]),
     "opencnn_convolutionForward_noalloc": (c_int, [c_void_p] * 3 + [c_int] * 5 + [c_void_p]),
     "opencnn_nchw_to_chwn": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "opencnn_kcrs_to_crsk": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),

@@ -87,6 +87,17 @@ def winograd_forward(input_chwn, workspace, output_khwn, N, C, H, W, K, *, preci
                                                        H, W, K, PRECISIONS[precision], stream)
 
 
+TC_KERNELS = {"auto": 0, "single": 1, "pair_local": 2, "pair_exchange": 3}
+
+
+def winograd_forward_kernel(input_chwn, workspace, output_khwn, N, C, H, W, K, *, precision, kernel, stream=0,
+                            variant="OPTSTS64") -> int:
+    """The tensor-core fused kernel with an explicit choice of kernel (opencnn_winograd_forward_kernel)."""
+    return _lib.load(variant).opencnn_winograd_forward_kernel(_ptr(input_chwn), _ptr(workspace), _ptr(output_khwn), N,
+                                                              C, H, W, K, PRECISIONS[precision], TC_KERNELS[kernel],
+                                                              stream)
+
+
 def nchw_to_chwn(src, dst, N, C, H, W, *, stream=0, variant="OPTSTS64") -> int:
     return _lib.load(variant).opencnn_nchw_to_chwn(_ptr(src), _ptr(dst), N, C, H, W, stream)
 

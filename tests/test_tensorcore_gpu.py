@@ -139,3 +139,37 @@ def test_tensor_core_error_at_benchmark_sizes(oracle, libs, precision, shape):
     assert api.conv3x3(dx, dg, dy2, dws, N, C, HW, HW, K, precision=precision) == 0
     torch.cuda.synchronize()
     assert torch.equal(dy, dy2)
+
+
+# Every tensor-core kernel on its own, chosen by the caller (opencnn_winograd_forward_kernel), whatever the
+# library's own rule would take: small and deep problems, an odd number of 32-image blocks, a ragged last block,
+# K not a multiple of 128, channel counts that are not a multiple of the K-step.
+KERNEL_SHAPES = [(32, 16, 128, 8, 8), (64, 40, 192, 5, 9), (96, 32, 256, 6, 6), (64, 512, 128, 4, 4), (128, 64, 64, 14, 14),
+                 (72, 48, 64, 5, 7), (104, 515, 128, 3, 3), (8, 16, 128, 4, 4), (160, 24, 320, 7, 7)]
+
+
+@pytest.mark.parametrize("kernel", ["single", "pair_local", "pair_exchange"])
+@pytest.mark.parametrize("precision", ["tf32", "bf16"])
+def test_each_tensor_core_kernel(oracle, libs, precision, kernel):
+    rnd = oracle.round_tf32 if precision == "tf32" else oracle.round_bf16
+    for (N, C, K, H, W) in KERNEL_SHAPES:
+        x = rnd(oracle.input_chwn(N, C, H, W)).reshape(C, H, W, N)
+        g = rnd(oracle.filter_crsk(C, K)).reshape(C, 3, 3, K)
+        dx, dg = torch.from_numpy(x).cuda(), torch.from_numpy(g).cuda()
+        dws = torch.empty((C, 4, 4, K), device="cuda")
+        assert api.filter_transform(dg, dws, C, K, precision=precision) == 0
+        outs = []
+        for _ in range(2):
+            dy = torch.full((K, H, W, N), float("nan"), device="cuda")
+            assert api.winograd_forward_kernel(dx, dws, dy, N, C, H, W, K, precision=precision, kernel=kernel) == 0
+            assert api.last_device_status() == 0, (kernel, precision, (N, C, K, H, W))
+            outs.append(dy)
+        assert torch.equal(outs[0], outs[1]), "not repeatable"
+        y = outs[0].cpu().numpy()
+        assert np.isfinite(y).all(), (kernel, precision, (N, C, K, H, W))
+        model = oracle.tc_model(x, g, precision)
+        rms = float(np.sqrt(np.mean(model.astype(np.float64) ** 2)))
+        worst = float(np.abs(y - model).max())
+        assert worst <= MODEL_REL * max(rms, 1e-30), f"{kernel} {precision} {(N, C, K, H, W)}: {worst / rms:.3e} of rms"
+    bad = torch.zeros(16, device="cuda")
+    assert api.winograd_forward_kernel(bad, bad, bad, 32, 8, 4, 4, 64, precision="fp32", kernel=kernel) != 0
