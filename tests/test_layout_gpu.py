@@ -9,7 +9,9 @@ from opencnn_b200 import api  # noqa: E402
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("shape", [(32, 8, 7, 7), (64, 24, 5, 9), (33, 3, 17, 2), (128, 64, 56, 56)])
+# both extents multiples of 4 (the 128-bit kernel, with partial tiles), an odd batch and an odd C*H*W (the
+# element-wise kernel), and the benchmark's largest tensor
+@pytest.mark.parametrize("shape", [(32, 8, 7, 7), (64, 24, 5, 9), (33, 3, 17, 2), (32, 3, 7, 7), (68, 4, 9, 13), (128, 64, 56, 56)])
 def test_nchw_to_chwn_and_back(libs, shape):
     N, C, H, W = shape
     x = torch.randn(N, C, H, W, device="cuda")
@@ -23,8 +25,9 @@ def test_nchw_to_chwn_and_back(libs, shape):
     assert torch.equal(back, x)
 
 
-def test_kcrs_to_crsk(libs):
-    K, C = 192, 40
+@pytest.mark.parametrize("kc", [(192, 40), (64, 3), (130, 7)])
+def test_kcrs_to_crsk(libs, kc):
+    K, C = kc
     w = torch.randn(K, C, 3, 3, device="cuda")
     crsk = torch.empty((C, 3, 3, K), device="cuda")
     assert api.kcrs_to_crsk(w, crsk, K, C) == 0
