@@ -16,6 +16,7 @@
 #include "wino_tc.cuh"
 #include "wino_tc2.cuh"
 #include "wino_tc3.cuh"
+#include "wino_tc64.cuh"
 
 #if defined(BASE)
 #define OCB_VARIANT ocb::kBase
@@ -156,6 +157,8 @@ cudaError_t device_state(DeviceState **out) {
         err = cudaOccupancyMaxActiveClusters(&st.max_clusters3[1], ocb::wino_tc3_kernel<ocb::kTcTf32>, &cfg);
       }
     }
+    if (err == cudaSuccess)
+      err = cudaFuncSetAttribute(ocb::wino_tc64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ocb::kT64SmemBytes);
     if (err == cudaSuccess) err = cudaGetSymbolAddress(reinterpret_cast<void **>(&st.status_ptr), g_status);
     st.init_error = err;
   });
@@ -443,6 +446,55 @@ cudaError_t launch_wino_tc3(const float *input, const float *workspace, float *o
   return cudaGetLastError();
 }
 
+// BF16 layers with at most 64 filters: two 32-image blocks share the 128 accumulator rows (wino_tc64.cuh).
+cudaError_t launch_wino_tc64(const float *input, const float *workspace, float *output, int N, int C, int H, int W,
+                             int K, cudaStream_t stream) {
+  if (K > 64) return cudaErrorInvalidValue;
+  DeviceState *st = nullptr;
+  cudaError_t e = device_state(&st);
+  if (e != cudaSuccess) return e;
+  EncodeTiledFn enc = encode_fn();
+  if (!enc) return cudaErrorNotSupported;
+  CUtensorMap tm_in, tm_u;
+  {
+    cuuint64_t dims[4] = {(cuuint64_t)N, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)C};
+    cuuint64_t strides[3] = {(cuuint64_t)N * 4, (cuuint64_t)W * N * 4, (cuuint64_t)H * W * N * 4};
+    cuuint32_t box[4] = {(cuuint32_t)ocb::kTcN, 4, 4, 16};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    if (enc(&tm_in, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(input), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return cudaErrorInvalidValue;
+  }
+  {
+    // workspace [C][16][K] bf16 viewed as {filter within a 128-byte row, channel, 128-byte row, position}; one row block
+    cuuint64_t dims[4] = {64, (cuuint64_t)C, (cuuint64_t)K / 64, 16};
+    cuuint64_t strides[3] = {(cuuint64_t)16 * K * 2, 128, (cuuint64_t)K * 2};
+    cuuint32_t box[4] = {64, 16, 1, 16};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    if (enc(&tm_u, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<float *>(workspace), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+      return cudaErrorInvalidValue;
+  }
+  ocb::WinoParams p;
+  p.y = output;
+  p.N = N; p.C = C; p.K = K; p.H = H; p.W = W;
+  p.tiles_h = (H + 1) / 2;
+  p.tiles_w = (W + 1) / 2;
+  p.n_blocks = (N + ocb::kTcN - 1) / ocb::kTcN;
+  p.k_blocks = 1;
+  const long long tiles = (long long)p.tiles_h * p.tiles_w * ((p.n_blocks + 1) / 2);
+  if (tiles > 0x7fffffffll / 8) return cudaErrorInvalidValue;
+  p.total_tiles = (int)tiles;
+  p.split_from = p.total_items = p.total_tiles;
+  p.chunks_per_tile = (C + 15) / 16;
+  p.status = st->status_ptr;
+  const int grid = p.total_tiles < st->sm_count ? p.total_tiles : st->sm_count;
+  ocb::wino_tc64_kernel<<<grid, ocb::kT64Threads, ocb::kT64SmemBytes, stream>>>(tm_in, tm_u, p);
+  return cudaGetLastError();
+}
+
 // Which tensor-core kernel a problem gets.  Both compute the same thing.  The CTA-pair kernel
 // (wino_tc2.cuh) has the cheaper main loop (half as many, twice as wide MMAs) but a dearer
 // epilogue (two CTAs meet through L2), so it wins where a tile has many K-steps and the MMAs are
@@ -455,7 +507,11 @@ cudaError_t launch_tc(const float *input, const float *workspace, float *output,
   if (kernel == OPENCNN_TC_SINGLE_CTA) return launch_wino_tc<DT>(input, workspace, output, N, C, H, W, K, stream);
   if (kernel == OPENCNN_TC_PAIR_LOCAL) return launch_wino_tc2<DT>(input, workspace, output, N, C, H, W, K, stream);
   if (kernel == OPENCNN_TC_PAIR_EXCHANGE) return launch_wino_tc3<DT>(input, workspace, output, N, C, H, W, K, stream);
+  if (kernel == OPENCNN_TC_STACKED_BLOCKS)
+    return DT == ocb::kTcBf16 ? launch_wino_tc64(input, workspace, output, N, C, H, W, K, stream) : cudaErrorInvalidValue;
   if (kernel != OPENCNN_TC_AUTO) return cudaErrorInvalidValue;
+  // at most 64 filters and more than one 32-image block: two blocks share the accumulator rows (BF16 only)
+  if (DT == ocb::kTcBf16 && K <= 64 && N > ocb::kTcN) return launch_wino_tc64(input, workspace, output, N, C, H, W, K, stream);
   const int k_steps = (C + ocb::TcCfg<DT>::kKC - 1) / ocb::TcCfg<DT>::kKC;
   const bool pair = DT == ocb::kTcTf32 && k_steps >= 64 && N >= 64;
   return pair ? launch_wino_tc2<DT>(input, workspace, output, N, C, H, W, K, stream)

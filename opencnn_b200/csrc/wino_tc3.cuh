@@ -35,8 +35,8 @@
 //                          the transform warps' barrier) and the peer's 8 KB landed (tx bytes)
 //   v_empty                this CTA's MMAs on the V stage have completed (tcgen05.commit)
 //   peer_v_empty           the PEER's MMAs on ITS V stage have completed, so this CTA may copy
-//                          there again; relayed by the peer's first MMA thread with a relaxed
-//                          remote arrive (it carries no data, only "you may overwrite")
+//                          there again: the peer's MMA threads commit to this barrier too (the
+//                          address of a tcgen05.commit is a shared::cluster address)
 // The CTAs meet again in the epilogue: the output transform is linear in the 16 positions, so
 // each CTA forms the partial result of its 8 positions; CTA r stores its partial for image block
 // r, signals the peer through an mbarrier in the peer's shared memory, and for the other block
@@ -46,7 +46,7 @@
 //
 // Warp roles, aligned to warpgroups of four warps because setmaxnreg is a warpgroup instruction:
 //   warps 0-3    one thread each: raw-patch loader, filter loader, two MMA issuers (four positions
-//                each; warp 2 also owns the TMEM allocation and relays)           -> 40 registers
+//                each; warp 2 also owns the TMEM allocation)                      -> 40 registers
 //   warps 4-11   input transform (BF16: all eight per K-step, one (channel, image pair) per
 //                thread; TF32: the two warpgroups take K-steps alternately)       -> 88 registers
 //   warps 12-19  epilogue, two warps per TMEM lane quarter                        -> 128 registers
@@ -74,11 +74,10 @@ template <int DT> struct P3Cfg {
   static constexpr uint32_t kRawBytes = kKC * 16 * 32 * 4;            // [c][4 h][4 w][32 n] fp32, this CTA's image block
   // Rings: raw patches, filters (U), transformed input (V, with one outgoing staging buffer per
   // stage).  V is the deepest: a V stage is refilled across the cluster, so its turn-around
-  // includes a relay and a copy.  The relay scheme needs kVStages > kUStages (see the MMA issuer).
+  // includes a copy between the two SMs.
   static constexpr int kRawStages = DT == kTcBf16 ? 2 : 4;
   static constexpr int kUStages = 2;
   static constexpr int kVStages = 4;
-  static_assert(kVStages > kUStages, "the peer learns of a free V stage only after the U ring has turned");
   // transform threads that work on one K-step: BF16 all 256, TF32 one warpgroup (K-steps alternate)
   static constexpr int kThreadsPerStep = DT == kTcBf16 ? 256 : 128;
   static constexpr size_t kSmemBytes = (size_t)kRawStages * kRawBytes + (size_t)kUStages * kP3UBytes +
@@ -187,7 +186,7 @@ __device__ __forceinline__ void p3_body(const CUtensorMap &tm_in, const CUtensor
     for (int s = 0; s < SV; ++s) {
       mbar_init(smem_u32(v_ready + s), 1);                         // own half (one arrive) + the peer's bytes
       mbar_init(smem_u32(v_empty + s), 2);
-      mbar_init(smem_u32(peer_v_empty + s), 1);                    // the peer's first MMA thread relays
+      mbar_init(smem_u32(peer_v_empty + s), 2);                    // the peer's two MMA threads commit here as well
     }
     mbar_init(smem_u32(peer_ready + 0), kP3EpilogueWarps);
     mbar_init(smem_u32(peer_ready + 1), kP3EpilogueWarps);
@@ -254,21 +253,11 @@ __device__ __forceinline__ void p3_body(const CUtensorMap &tm_in, const CUtensor
         const uint64_t a_desc0 = DT == kTcBf16 ? smem_desc(smem_u32(u_s), KC * 128, 1024, 2) : smem_desc(smem_u32(u_s), KC * 128, 512, 1);
         const uint64_t b_desc0 = DT == kTcBf16 ? smem_desc(smem_u32(v_s), kP3HalfBytes, 512, 4) : smem_desc(smem_u32(v_s), kP3HalfBytes, 512, 1);
         const uint32_t peer_v_empty0 = mapa_u32(smem_u32(peer_v_empty), PEER);
-        int ci = 0, seq = 0, relayed = 0;
+        int ci = 0, seq = 0;
         for (int g = 0; g < total_chunks; ++g) {
           const int su = g % SU, sv = g % SV;
           // A wait that gave up: stop issuing.
           if (!mbar_wait(smem_u32(u_full + su), (g / SU) & 1, dead, p.status)) break;
-          if (me == 0) {
-            // Relay: tell the peer which of this CTA's V stages its copies may overwrite again.  The filter
-            // slice of this K-step could only be loaded after the MMAs of K-step g - kUStages had completed,
-            // so those stages are free by now; test_wait never blocks.  The peer's transform of K-step g + 1
-            // needs the stage of K-step g + 1 - kVStages, which is older (kVStages > kUStages): no deadlock.
-            while (relayed < g && mbar_test_wait(smem_u32(v_empty + relayed % SV), (relayed / SV) & 1)) {
-              mbar_arrive_remote_relaxed(peer_v_empty0 + 8u * (uint32_t)(relayed % SV));
-              ++relayed;
-            }
-          }
           if (!mbar_wait(smem_u32(v_ready + sv), (g / SV) & 1, dead, p.status)) break;     // both halves of V in place
           if (ci == 0 && seq > 0 && !mbar_wait(smem_u32(acc_empty), (seq - 1) & 1, dead, p.status)) break;   // TMEM drained
           tc_fence_after();
@@ -281,6 +270,7 @@ __device__ __forceinline__ void p3_body(const CUtensorMap &tm_in, const CUtensor
           }
           tc_commit(smem_u32(u_empty + su));
           tc_commit(smem_u32(v_empty + sv));
+          tc_commit(peer_v_empty0 + 8u * (uint32_t)sv);      // the same completion, signalled in the peer's shared memory
           if (++ci == cpt) {
             tc_commit(smem_u32(acc_full));
             ci = 0;

@@ -17,11 +17,18 @@ import argparse
 import sys
 
 
+def api_kernels():
+    from .api import TC_KERNELS
+    return TC_KERNELS
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("dims", nargs="*", type=int, help="N C H W K C R S (defaults 128 256 14 14 256 256 3 3)")
     ap.add_argument("--variant", default="OPTSTS64")
     ap.add_argument("--precision", default="fp32", choices=["fp32", "tf32", "bf16"])
+    ap.add_argument("--tc-kernel", default="auto", choices=sorted(api_kernels()),
+                    help="with --precision tf32/bf16: which tensor-core kernel runs (default: the library's own choice)")
     ap.add_argument("--header", action="store_true")
     ap.add_argument("--iterations", type=int, default=100)
     args = ap.parse_args(argv)
@@ -50,7 +57,11 @@ def main(argv=None) -> int:
         return 1
 
     def ours():
-        return api.conv3x3(xc, wc, y, ws, N, C, H, W, K, precision=args.precision, variant=args.variant)
+        if args.tc_kernel == "auto" or args.precision == "fp32":
+            return api.conv3x3(xc, wc, y, ws, N, C, H, W, K, precision=args.precision, variant=args.variant)
+        err = api.filter_transform(wc, ws, C, K, precision=args.precision, variant=args.variant)
+        return err or api.winograd_forward_kernel(xc, ws, y, N, C, H, W, K, precision=args.precision,
+                                                  kernel=args.tc_kernel, variant=args.variant)
 
     err = ours()
     if err != 0:
