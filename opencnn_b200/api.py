@@ -87,7 +87,7 @@ def winograd_forward(input_chwn, workspace, output_khwn, N, C, H, W, K, *, preci
                                                        H, W, K, PRECISIONS[precision], stream)
 
 
-TC_KERNELS = {"auto": 0, "single": 1, "pair_local": 2, "pair_exchange": 3, "stacked": 4}
+TC_KERNELS = {"auto": 0, "single": 1, "pair_local": 2, "stacked": 3}
 
 
 def winograd_forward_kernel(input_chwn, workspace, output_khwn, N, C, H, W, K, *, precision, kernel, stream=0,

@@ -15,7 +15,6 @@
 #include "wino_fp32.cuh"
 #include "wino_tc.cuh"
 #include "wino_tc2.cuh"
-#include "wino_tc3.cuh"
 #include "wino_tc64.cuh"
 
 #if defined(BASE)
@@ -43,7 +42,6 @@ struct DeviceState {
   cudaError_t init_error = cudaSuccess;
   int sm_count = 0;
   int max_clusters[2] = {0, 0};   // co-resident CTA pairs of wino_tc2_kernel<BF16 / TF32>
-  int max_clusters3[2] = {0, 0};  // co-resident CTA pairs of wino_tc3_kernel<BF16 / TF32>
   int *status_ptr = nullptr;
 };
 DeviceState g_dev[kMaxDevices];
@@ -123,38 +121,6 @@ cudaError_t device_state(DeviceState **out) {
       if (err == cudaSuccess) {
         cfg.dynamicSmemBytes = ocb::P2Cfg<ocb::kTcTf32>::kSmemBytes;
         err = cudaOccupancyMaxActiveClusters(&st.max_clusters[1], ocb::wino_tc2_kernel<ocb::kTcTf32>, &cfg);
-      }
-    }
-    if (err == cudaSuccess)
-      err = cudaFuncSetAttribute(ocb::wino_tc3_kernel<ocb::kTcBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)ocb::P3Cfg<ocb::kTcBf16>::kSmemBytes);
-    if (err == cudaSuccess)
-      err = cudaFuncSetAttribute(ocb::wino_tc3_kernel<ocb::kTcTf32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                 (int)ocb::P3Cfg<ocb::kTcTf32>::kSmemBytes);
-    if (err == cudaSuccess) {
-      // like the fp32 kernel, the exchange kernel redistributes registers with setmaxnreg: refuse a build whose
-      // register pool is smaller than the budgets add up to
-      constexpr int kBudget3 = 128 * ocb::kP3ControlRegs + 256 * ocb::kP3TransformRegs + 256 * ocb::kP3EpilogueRegs;
-      cudaFuncAttributes fa;
-      err = cudaFuncGetAttributes(&fa, ocb::wino_tc3_kernel<ocb::kTcBf16>);
-      if (err == cudaSuccess && fa.numRegs * ocb::kP3Threads < kBudget3) err = cudaErrorLaunchOutOfResources;
-      if (err == cudaSuccess) err = cudaFuncGetAttributes(&fa, ocb::wino_tc3_kernel<ocb::kTcTf32>);
-      if (err == cudaSuccess && fa.numRegs * ocb::kP3Threads < kBudget3) err = cudaErrorLaunchOutOfResources;
-    }
-    if (err == cudaSuccess) {
-      cudaLaunchConfig_t cfg = {};
-      cfg.gridDim = dim3(2 * (unsigned)st.sm_count);
-      cfg.blockDim = dim3(ocb::kP3Threads);
-      cudaLaunchAttribute attr;
-      attr.id = cudaLaunchAttributeClusterDimension;
-      attr.val.clusterDim.x = 2; attr.val.clusterDim.y = 1; attr.val.clusterDim.z = 1;
-      cfg.attrs = &attr;
-      cfg.numAttrs = 1;
-      cfg.dynamicSmemBytes = ocb::P3Cfg<ocb::kTcBf16>::kSmemBytes;
-      err = cudaOccupancyMaxActiveClusters(&st.max_clusters3[0], ocb::wino_tc3_kernel<ocb::kTcBf16>, &cfg);
-      if (err == cudaSuccess) {
-        cfg.dynamicSmemBytes = ocb::P3Cfg<ocb::kTcTf32>::kSmemBytes;
-        err = cudaOccupancyMaxActiveClusters(&st.max_clusters3[1], ocb::wino_tc3_kernel<ocb::kTcTf32>, &cfg);
       }
     }
     if (err == cudaSuccess)
@@ -389,63 +355,6 @@ cudaError_t launch_wino_tc2(const float *input, const float *workspace, float *o
   return cudaGetLastError();
 }
 
-// Exchange kernel: clusters of two CTAs share a tile of 128 filters x 64 images, each transforms its own
-// 32 images and writes half of the result into the peer's shared memory (wino_tc3.cuh).
-template <int DT>
-cudaError_t launch_wino_tc3(const float *input, const float *workspace, float *output, int N, int C, int H, int W,
-                            int K, cudaStream_t stream) {
-  DeviceState *st = nullptr;
-  cudaError_t e = device_state(&st);
-  if (e != cudaSuccess) return e;
-  EncodeTiledFn enc = encode_fn();
-  if (!enc) return cudaErrorNotSupported;
-  constexpr int KC = ocb::P3Cfg<DT>::kKC;
-  constexpr bool bf16 = DT == ocb::kTcBf16;
-  constexpr cuuint64_t esz = bf16 ? 2 : 4;
-  constexpr cuuint32_t row_elems = bf16 ? 64 : 32;
-  const int max_clusters = st->max_clusters3[bf16 ? 0 : 1];
-  if (max_clusters <= 0) return cudaErrorNotSupported;
-
-  CUtensorMap tm_in, tm_u;
-  {
-    cuuint64_t dims[4] = {(cuuint64_t)N, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)C};
-    cuuint64_t strides[3] = {(cuuint64_t)N * 4, (cuuint64_t)W * N * 4, (cuuint64_t)H * W * N * 4};
-    cuuint32_t box[4] = {32, 4, 4, (cuuint32_t)KC};                       // one CTA's image block
-    cuuint32_t estr[4] = {1, 1, 1, 1};
-    if (enc(&tm_in, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(input), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-      return cudaErrorInvalidValue;
-  }
-  {
-    cuuint64_t dims[4] = {row_elems, (cuuint64_t)C, (cuuint64_t)K / row_elems, 16};
-    cuuint64_t strides[3] = {(cuuint64_t)16 * K * esz, 128, (cuuint64_t)K * esz};
-    cuuint32_t box[4] = {row_elems, (cuuint32_t)KC, (cuuint32_t)(ocb::kTcM / row_elems), 8};   // one CTA's eight positions
-    cuuint32_t estr[4] = {1, 1, 1, 1};
-    if (enc(&tm_u, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4,
-            const_cast<float *>(workspace), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            bf16 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-      return cudaErrorInvalidValue;
-  }
-  ocb::WinoParams p;
-  p.y = output;
-  p.N = N; p.C = C; p.K = K; p.H = H; p.W = W;
-  p.tiles_h = (H + 1) / 2;
-  p.tiles_w = (W + 1) / 2;
-  p.n_blocks = (N + ocb::kTcN - 1) / ocb::kTcN;
-  p.k_blocks = (K + ocb::kTcM - 1) / ocb::kTcM;
-  const long long tiles = (long long)p.tiles_h * p.tiles_w * ((p.n_blocks + 1) / 2) * p.k_blocks;
-  if (tiles > 0x7fffffffll / 8) return cudaErrorInvalidValue;
-  p.total_tiles = (int)tiles;
-  p.split_from = p.total_items = p.total_tiles;
-  p.chunks_per_tile = (C + KC - 1) / KC;
-  p.status = st->status_ptr;
-  const int clusters = p.total_tiles < max_clusters ? p.total_tiles : max_clusters;
-  ocb::wino_tc3_kernel<DT><<<2 * clusters, ocb::kP3Threads, ocb::P3Cfg<DT>::kSmemBytes, stream>>>(tm_in, tm_u, p);
-  return cudaGetLastError();
-}
-
 // BF16 layers with at most 64 filters: two 32-image blocks share the 128 accumulator rows (wino_tc64.cuh).
 cudaError_t launch_wino_tc64(const float *input, const float *workspace, float *output, int N, int C, int H, int W,
                              int K, cudaStream_t stream) {
@@ -506,7 +415,6 @@ cudaError_t launch_tc(const float *input, const float *workspace, float *output,
                       cudaStream_t stream, int kernel = OPENCNN_TC_AUTO) {
   if (kernel == OPENCNN_TC_SINGLE_CTA) return launch_wino_tc<DT>(input, workspace, output, N, C, H, W, K, stream);
   if (kernel == OPENCNN_TC_PAIR_LOCAL) return launch_wino_tc2<DT>(input, workspace, output, N, C, H, W, K, stream);
-  if (kernel == OPENCNN_TC_PAIR_EXCHANGE) return launch_wino_tc3<DT>(input, workspace, output, N, C, H, W, K, stream);
   if (kernel == OPENCNN_TC_STACKED_BLOCKS)
     return DT == ocb::kTcBf16 ? launch_wino_tc64(input, workspace, output, N, C, H, W, K, stream) : cudaErrorInvalidValue;
   if (kernel != OPENCNN_TC_AUTO) return cudaErrorInvalidValue;
