@@ -1,9 +1,17 @@
-// Measurement aid, not part of the operator: the FP32 FMA rate this GPU sustains, used as the
-// roofline denominator of the FFMA path (no driver-supplied figure exists for the FP32 pipe).
-// One persistent CTA per SM, 8 warps, 32 independent packed accumulators per lane issuing
-// fma.rn.f32x2 back to back.  Two operand patterns: see the kernel.
+// Measurement aids, not part of the operator.
+//  * The FP32 FMA rate this GPU sustains, used as the roofline denominator of the FFMA path (no
+//    driver-supplied figure exists for the FP32 pipe): one persistent CTA per SM, 8 warps, 32
+//    independent packed accumulators per lane issuing fma.rn.f32x2 back to back.  Two operand
+//    patterns: see the kernel.
+//  * The same loop with other instructions mixed in: does a packed FMA leave issue slots free?
+//  * How long one SM waits for a TMA load of a filter slice out of L2 (tiled box or linear bulk
+//    copy), with one to three loads in flight: the latency that a two-stage ring cannot hide.
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <cstdint>
+#include <vector>
+
+#include "ptx.cuh"
 
 namespace {
 
@@ -83,3 +91,173 @@ static int run_probe(bool busy, int iters, int reps, double *tflops) {
 extern "C" int opencnn_peaks_fp32_tflops(int iters, int reps, double *tflops) { return run_probe(false, iters, reps, tflops); }
 // The same loop on operands that keep changing (see the kernel's comment).
 extern "C" int opencnn_peaks_fp32_tflops_busy(int iters, int reps, double *tflops) { return run_probe(true, iters, reps, tflops); }
+
+// ---- issue-port probe ---------------------------------------------------------------------------
+namespace {
+// 64 packed FMAs per loop body plus EXTRA independent instructions of one KIND spread between them:
+// KIND 0 integer xor, 1 register move, 2 scalar add.f32 (which shares the FMA pipe).
+template <int EXTRA, int KIND>
+__global__ void __launch_bounds__(256, 1) issue_probe_kernel(float *out, int iters, float a, float b) {
+  uint64_t acc[32], av, bv;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(av) : "f"(0.5f * a), "f"(1.5f * a));
+  asm("mov.b64 %0, {%1, %2};" : "=l"(bv) : "f"(2.f * b), "f"(3.f * b));
+#pragma unroll
+  for (int i = 0; i < 32; ++i) asm("mov.b64 %0, {%1, %2};" : "=l"(acc[i]) : "f"((float)i), "f"((float)(i + threadIdx.x)));
+  unsigned x[8];
+  float fx[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { x[i] = threadIdx.x + i; fx[i] = (float)i; }
+  for (int it = 0; it < iters; ++it) {
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        asm volatile("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc[i]) : "l"(av), "l"(bv));
+        if ((i + 32 * r) * EXTRA / 64 != (i + 32 * r + 1) * EXTRA / 64) {
+          if (KIND == 0) asm volatile("xor.b32 %0, %0, %1;" : "+r"(x[i & 7]) : "r"(x[(i + 1) & 7]));
+          else if (KIND == 1) asm volatile("mov.b32 %0, %1;" : "=r"(x[i & 7]) : "r"(x[(i + 3) & 7]));
+          else asm volatile("add.rn.f32 %0, %0, %1;" : "+f"(fx[i & 7]) : "f"(a));
+        }
+      }
+    }
+  }
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) { float lo, hi; asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(acc[i])); s += lo + hi; }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) s += (float)x[i] + fx[i];
+  out[blockIdx.x * blockDim.x + threadIdx.x] = s;
+}
+
+template <int EXTRA, int KIND> float time_issue_probe(float *out, int sms, int iters) {
+  cudaEvent_t t0, t1;
+  cudaEventCreate(&t0);
+  cudaEventCreate(&t1);
+  float best = 1e30f;
+  for (int r = 0; r < 4; ++r) {
+    cudaEventRecord(t0, 0);
+    issue_probe_kernel<EXTRA, KIND><<<sms, 256>>>(out, iters, 1.0001f, 0.5f);
+    cudaEventRecord(t1, 0);
+    if (cudaEventSynchronize(t1) != cudaSuccess) break;
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, t0, t1);
+    if (r > 0 && ms < best) best = ms;
+  }
+  cudaEventDestroy(t0);
+  cudaEventDestroy(t1);
+  return best;
+}
+}  // namespace
+
+// Milliseconds for `iters` loop bodies of 64 packed FMAs + `extra` (0, 8, 16, 32 or 64) instructions of `kind`
+// (0 xor, 1 mov, 2 add.f32) on every SM, 8 warps each.  Returns a cudaError_t code (1 for unsupported arguments).
+extern "C" int opencnn_peaks_issue_probe(int extra, int kind, int iters, double *ms) {
+  int dev = 0, sms = 0;
+  if (!ms || cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+    return (int)cudaErrorInvalidValue;
+  float *out = nullptr;
+  if (cudaMalloc(&out, (size_t)sms * 256 * sizeof(float)) != cudaSuccess) return (int)cudaErrorMemoryAllocation;
+  float t = -1.f;
+#define OCB_CASE(E, K) if (extra == E && kind == K) t = time_issue_probe<E, K>(out, sms, iters);
+  OCB_CASE(0, 0) OCB_CASE(8, 0) OCB_CASE(16, 0) OCB_CASE(32, 0) OCB_CASE(64, 0)
+  OCB_CASE(16, 1) OCB_CASE(32, 1) OCB_CASE(16, 2) OCB_CASE(32, 2)
+#undef OCB_CASE
+  cudaFree(out);
+  if (t < 0.f) return (int)cudaErrorInvalidValue;
+  *ms = t;
+  return (int)cudaGetLastError();
+}
+
+// ---- TMA latency probe --------------------------------------------------------------------------
+namespace {
+__device__ __forceinline__ void bulk_load_linear(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cta.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+// One thread per CTA issues loads of `bytes` into a ring of three 64 KB slots and waits for the load issued
+// `depth - 1` iterations earlier.  Tiled: the 4-D box {64 bf16, 16 channels, 2 row blocks, bytes / 4096 positions}
+// of a transformed-filter workspace [C][16][K]; linear: the same number of contiguous bytes.
+__global__ void __launch_bounds__(128, 1) tma_latency_kernel(const __grid_constant__ CUtensorMap map, const uint8_t *lin, size_t lin_bytes,
+                                                             uint32_t bytes, int tiled, int depth, int iters, int n_ci, long long *out,
+                                                             int *status) {
+  extern __shared__ __align__(1024) uint8_t sm[];
+  uint64_t *bars = reinterpret_cast<uint64_t *>(sm + 3 * 65536);
+  __shared__ int dead;
+  if (threadIdx.x == 0) {
+    dead = 0;
+    for (int s = 0; s < 3; ++s) ocb::mbar_init(ocb::smem_u32(bars + s), 1);
+    ocb::mbar_fence_init();
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const long long t0 = clock64();
+    for (int it = 0; it < iters + depth; ++it) {
+      if (it < iters) {
+        const int s = it % 3;
+        const uint32_t bar = ocb::smem_u32(bars + s), dst = ocb::smem_u32(sm + s * 65536);
+        ocb::mbar_arrive_expect_tx(bar, bytes);
+        const int ci = (it * 7 + (int)blockIdx.x) % n_ci;
+        if (tiled) ocb::tma_load_4d(dst, &map, bar, 0, ci * 16, 0, 0);
+        else bulk_load_linear(dst, lin + ((size_t)ci * bytes) % (lin_bytes - bytes), bytes, bar);
+      }
+      const int w = it - depth + 1;
+      if (w >= 0 && w < iters && !ocb::mbar_wait(ocb::smem_u32(bars + w % 3), (w / 3) & 1, &dead, status)) break;
+    }
+    out[blockIdx.x] = clock64() - t0;
+  }
+}
+__device__ int g_probe_status = 0;
+}  // namespace
+
+// Average cycles per load (issue to completion, `depth` loads in flight) over `grid` CTAs, one per SM.
+// bytes: 32768 or 65536; tiled: 1 = 4-D TMA box, 0 = linear bulk copy.  Returns a cudaError_t code.
+extern "C" int opencnn_peaks_tma_latency(int bytes, int tiled, int depth, int iters, int grid, double *cycles_per_load) {
+  if (!cycles_per_load || (bytes != 32768 && bytes != 65536) || depth < 1 || depth > 3 || iters < 1 || grid < 1)
+    return (int)cudaErrorInvalidValue;
+  const int C = 1024, K = 128;                                  // bf16 workspace of 4 MB: stays in L2
+  const size_t ws_bytes = (size_t)C * 16 * K * 2;
+  uint8_t *ws = nullptr;
+  long long *out = nullptr;
+  int *status = nullptr;
+  cudaError_t e = cudaMalloc(&ws, ws_bytes);
+  if (e == cudaSuccess) e = cudaMemset(ws, 0, ws_bytes);
+  if (e == cudaSuccess) e = cudaMalloc(&out, (size_t)grid * sizeof(long long));
+  if (e == cudaSuccess) e = cudaGetSymbolAddress(reinterpret_cast<void **>(&status), g_probe_status);
+  CUtensorMap map;
+  if (e == cudaSuccess) {
+    void *fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    using Enc = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                             const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                             CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+      e = cudaErrorNotSupported;
+    else {
+      cuuint64_t dims[4] = {64, (cuuint64_t)C, (cuuint64_t)K / 64, 16};
+      cuuint64_t strides[3] = {(cuuint64_t)16 * K * 2, 128, (cuuint64_t)K * 2};
+      cuuint32_t box[4] = {64, 16, 2, (cuuint32_t)(bytes / 4096)};
+      cuuint32_t estr[4] = {1, 1, 1, 1};
+      if (reinterpret_cast<Enc>(fn)(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, ws, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        e = cudaErrorInvalidValue;
+    }
+  }
+  const size_t smem = 3 * 65536 + 64;
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(tma_latency_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e == cudaSuccess) {
+    for (int rep = 0; rep < 2; ++rep)                          // the first run warms L2 and the instruction cache
+      tma_latency_kernel<<<grid, 128, smem>>>(map, ws, ws_bytes, (uint32_t)bytes, tiled, depth, iters, C / 16, out, status);
+    e = cudaDeviceSynchronize();
+  }
+  if (e == cudaSuccess) {
+    std::vector<long long> h(grid);
+    e = cudaMemcpy(h.data(), out, (size_t)grid * sizeof(long long), cudaMemcpyDeviceToHost);
+    double s = 0.0;
+    for (long long v : h) s += (double)v;
+    *cycles_per_load = s / grid / iters;
+  }
+  if (ws) cudaFree(ws);
+  if (out) cudaFree(out);
+  return (int)e;
+}

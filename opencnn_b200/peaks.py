@@ -1,0 +1,67 @@
+"""Runs the measurement aids of csrc/peaks.cu and prints their tables:
+
+    python -m opencnn_b200.peaks
+
+* FP32 FMA rate (the roofline denominator of the fp32 path), with operands that barely change and
+  with operands that keep changing;
+* whether instructions mixed into a stream of packed FMAs cost issue slots;
+* how long one SM waits for a 32 / 64 KB TMA load out of L2 with one to three loads in flight.
+"""
+import ctypes
+import sys
+
+from .build import build_peaks
+
+
+def load():
+    lib = ctypes.CDLL(build_peaks())
+    d = ctypes.POINTER(ctypes.c_double)
+    lib.opencnn_peaks_fp32_tflops.argtypes = [ctypes.c_int, ctypes.c_int, d]
+    lib.opencnn_peaks_fp32_tflops_busy.argtypes = [ctypes.c_int, ctypes.c_int, d]
+    lib.opencnn_peaks_issue_probe.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, d]
+    lib.opencnn_peaks_tma_latency.argtypes = [ctypes.c_int] * 5 + [d]
+    return lib
+
+
+def _call(fn, *args):
+    out = ctypes.c_double(0.0)
+    err = fn(*args, ctypes.byref(out))
+    if err != 0:
+        raise RuntimeError(f"{fn.__name__}{args} returned cudaError {err}")
+    return out.value
+
+
+def issue_probe(lib, iters=20000):
+    """{(extra, kind): ms} for the loop of 64 packed FMAs + extra instructions (kind 0 xor, 1 mov, 2 add.f32)."""
+    cases = [(0, 0), (8, 0), (16, 0), (32, 0), (64, 0), (16, 1), (32, 1), (16, 2), (32, 2)]
+    return {c: _call(lib.opencnn_peaks_issue_probe, c[0], c[1], iters) for c in cases}
+
+
+def tma_latency(lib, grid, iters=400):
+    """{(bytes, tiled, depth): cycles per load}."""
+    return {(b, t, d): _call(lib.opencnn_peaks_tma_latency, b, t, d, iters, grid)
+            for b in (65536, 32768) for t in (1, 0) for d in (1, 2, 3)}
+
+
+def main() -> int:
+    import torch
+    if not torch.cuda.is_available():
+        print("needs a CUDA device", file=sys.stderr)
+        return 1
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    lib = load()
+    print(f"FP32 pipe, fma.rn.f32x2: {_call(lib.opencnn_peaks_fp32_tflops, 20000, 3):.1f} TFLOP/s (operands that barely change), "
+          f"{_call(lib.opencnn_peaks_fp32_tflops_busy, 20000, 3):.1f} TFLOP/s (operands that keep changing)")
+    kinds = ["xor", "mov", "add.f32"]
+    base = None
+    for (extra, kind), ms in issue_probe(lib).items():
+        base = base or ms
+        print(f"64 packed FMAs + {extra:2d} {kinds[kind]:8s}: {ms:.3f} ms  ({ms / base:.2f} x the plain loop)")
+    for grid in (1, sms):
+        for (b, t, d), cyc in tma_latency(lib, grid).items():
+            print(f"{grid:3d} SMs  {b // 1024} KB {'tiled box ' if t else 'linear    '} {d} in flight: {cyc:6.0f} cycles per load, {b / cyc:5.1f} B/clk")
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

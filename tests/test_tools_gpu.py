@@ -65,3 +65,19 @@ def test_wgrad_command_line_prints_the_reference_csv():
     bad = subprocess.run([sys.executable, "-m", "opencnn_b200.wgrad", "32", "64", "56", "56", "64", "64", "5", "5"],
                          cwd=ROOT, capture_output=True, text=True, timeout=600)
     assert bad.returncode == 1 and "not supported" in bad.stderr
+
+
+def test_peak_probes_relations():
+    """The measurement aids of csrc/peaks.cu: moves mixed into a packed-FMA stream are free, scalar adds are not;
+    a second TMA load in flight nearly halves the time per load."""
+    from opencnn_b200 import peaks
+    lib = peaks.load()
+    t = peaks.issue_probe(lib, iters=5000)
+    plain = t[(0, 0)]
+    assert t[(16, 1)] <= 1.05 * plain and t[(32, 0)] <= 1.06 * plain, t
+    assert t[(32, 2)] >= 1.10 * plain, t
+    assert t[(64, 0)] >= 1.3 * plain, t
+    lat = peaks.tma_latency(lib, grid=8, iters=200)
+    for b in (65536, 32768):
+        assert 300 < lat[(b, 1, 1)] < 5000, lat
+        assert lat[(b, 1, 2)] <= 0.75 * lat[(b, 1, 1)], lat
