@@ -261,3 +261,130 @@ extern "C" int opencnn_peaks_tma_latency(int bytes, int tiled, int depth, int it
   if (out) cudaFree(out);
   return (int)e;
 }
+
+// ---- tcgen05.mma issue-rate probe ---------------------------------------------------------------
+#include "wino_tc.cuh"   // tcgen05 helpers: tmem_alloc_512, tc_commit, smem_desc, fences
+
+namespace {
+struct MmaRateCfg {
+  uint32_t idesc;
+  uint32_t a_lbo, a_sbo, a_mode, b_lbo, b_sbo, b_mode;
+  uint32_t a_off[16], b_off[16];   // byte offsets of the 16 operand tiles inside the A and B regions
+  uint32_t n;                      // MMA N: accumulator j sits at TMEM column (j * n) % 512
+};
+constexpr uint32_t kRateABytes = 64 * 1024, kRateBBytes = 128 * 1024;
+
+// One thread per CTA issues `iters` groups of 16 MMAs (M = 128) on zero-filled shared memory, commits once and
+// waits; the other threads only clear shared memory.  Results are never read: only the issue-to-completion
+// time of the chain counts.  KIND 0 = kind::f16 (BF16, K = 16), 1 = kind::tf32 (K = 8).
+template <int KIND>
+__global__ void __launch_bounds__(128, 1) mma_rate_kernel(const MmaRateCfg cfg, int iters, long long *out, int *status) {
+  extern __shared__ __align__(1024) uint8_t sm[];
+  __shared__ uint32_t tmem_slot;
+  __shared__ __align__(8) uint64_t bar;
+  __shared__ int dead;
+  for (uint32_t i = threadIdx.x; i < (kRateABytes + kRateBBytes) / 16; i += blockDim.x)
+    reinterpret_cast<uint4 *>(sm)[i] = make_uint4(0, 0, 0, 0);
+  if (threadIdx.x == 0) {
+    dead = 0;
+    ocb::mbar_init(ocb::smem_u32(&bar), 1);
+    ocb::mbar_fence_init();
+  }
+  if (threadIdx.x < 32) ocb::tmem_alloc_512(ocb::smem_u32(&tmem_slot));
+  ocb::fence_proxy_async_smem();
+  ocb::tc_fence_before();
+  __syncthreads();
+  ocb::tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  if (threadIdx.x == 0) {
+    const uint32_t a0 = ocb::smem_u32(sm), b0 = a0 + kRateABytes;
+    uint64_t ad[16], bd[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j) {
+      ad[j] = ocb::smem_desc(a0 + cfg.a_off[j], cfg.a_lbo, cfg.a_sbo, cfg.a_mode);
+      bd[j] = ocb::smem_desc(b0 + cfg.b_off[j], cfg.b_lbo, cfg.b_sbo, cfg.b_mode);
+    }
+    const long long t0 = clock64();
+    for (int it = 0; it < iters; ++it) {
+#pragma unroll
+      for (int j = 0; j < 16; ++j)
+        ocb::tc_mma<KIND>(tmem + ((uint32_t)j * cfg.n) % 512u, ad[j], bd[j], cfg.idesc, 1u);
+    }
+    ocb::tc_commit(ocb::smem_u32(&bar));
+    ocb::mbar_wait(ocb::smem_u32(&bar), 0, &dead, status);
+    out[blockIdx.x] = clock64() - t0;
+  }
+  ocb::tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x < 32) ocb::tmem_dealloc_512(tmem);
+}
+}  // namespace
+
+// Average SM cycles per tcgen05.mma (cta_group::1, M = 128, fp32 accumulate) in a chain of 16 * iters MMAs issued
+// by one thread, over `grid` CTAs, one per SM.
+//   kind    0 = BF16 (K = 16 per MMA), 1 = TF32 (K = 8)
+//   n       MMA N: 32, 64, 128 or 256
+//   layout  0 = both operands MN-major as the fused kernels hold them (A 128-byte swizzle, B 64-byte swizzle for
+//               BF16; 128-byte swizzle with 32-byte atoms for TF32), 16 operand tiles at separate addresses;
+//           1 = both K-major, no swizzle (8 x 16-byte core matrices), rows of one K-step (32 bytes);
+//           2 = both K-major, 32-byte swizzle, rows of one K-step;
+//           3 = both K-major, 128-byte swizzle, rows of four K-steps (the usual GEMM operand layout).
+// Returns a cudaError_t code; -1 if a wait ran out.
+extern "C" int opencnn_peaks_mma_rate(int kind, int n, int layout, int iters, int grid, double *cycles_per_mma) {
+  if (!cycles_per_mma || kind < 0 || kind > 1 || (n != 32 && n != 64 && n != 128 && n != 256) || layout < 0 || layout > 3 ||
+      iters < 1 || grid < 1)
+    return (int)cudaErrorInvalidValue;
+  MmaRateCfg c{};
+  const uint32_t fmt = kind == 0 ? 1u : 2u, mn_major = layout == 0 ? 1u : 0u;
+  c.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (mn_major << 15) | (mn_major << 16) | ((uint32_t)(n >> 3) << 17) | (8u << 24);
+  c.n = (uint32_t)n;
+  uint32_t a_tile, b_tile, kdiv = 1, kstep = 0;
+  switch (layout) {
+    case 0:
+      if (kind == 0) { c.a_lbo = 2048; c.a_sbo = 1024; c.a_mode = 2; c.b_lbo = 1024; c.b_sbo = 512; c.b_mode = 4; }
+      else           { c.a_lbo = 1024; c.a_sbo = 512;  c.a_mode = 1; c.b_lbo = 1024; c.b_sbo = 512; c.b_mode = 1; }
+      a_tile = 4096; b_tile = 32u * n;
+      break;
+    case 1:
+      c.a_lbo = c.b_lbo = 128; c.a_sbo = c.b_sbo = 256; c.a_mode = c.b_mode = 0;
+      a_tile = 4096; b_tile = 32u * n;
+      break;
+    case 2:
+      c.a_lbo = c.b_lbo = 16; c.a_sbo = c.b_sbo = 256; c.a_mode = c.b_mode = 6;
+      a_tile = 4096; b_tile = 32u * n;
+      break;
+    default:
+      c.a_lbo = c.b_lbo = 16; c.a_sbo = c.b_sbo = 1024; c.a_mode = c.b_mode = 2;
+      a_tile = 16384; b_tile = 128u * n; kdiv = 4; kstep = 32;
+      break;
+  }
+  for (uint32_t j = 0; j < 16; ++j) {
+    c.a_off[j] = (j / kdiv) * a_tile + (j % kdiv) * kstep;
+    c.b_off[j] = (j / kdiv) * b_tile + (j % kdiv) * kstep;
+    if (c.a_off[j] + a_tile > kRateABytes || c.b_off[j] + b_tile > kRateBBytes) return (int)cudaErrorInvalidValue;
+  }
+  long long *out = nullptr;
+  int *status = nullptr;
+  cudaError_t e = cudaMalloc(&out, (size_t)grid * sizeof(long long));
+  if (e == cudaSuccess) e = cudaGetSymbolAddress(reinterpret_cast<void **>(&status), g_probe_status);
+  if (e == cudaSuccess) e = cudaMemset(status, 0, sizeof(int));
+  const size_t smem = kRateABytes + kRateBBytes;
+  auto kern = kind == 0 ? mma_rate_kernel<0> : mma_rate_kernel<1>;
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e == cudaSuccess) {
+    for (int rep = 0; rep < 2; ++rep) kern<<<grid, 128, smem>>>(c, iters, out, status);
+    e = cudaDeviceSynchronize();
+  }
+  int st = 0;
+  if (e == cudaSuccess) e = cudaMemcpy(&st, status, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e == cudaSuccess) {
+    std::vector<long long> h(grid);
+    e = cudaMemcpy(h.data(), out, (size_t)grid * sizeof(long long), cudaMemcpyDeviceToHost);
+    double s = 0.0;
+    for (long long v : h) s += (double)v;
+    *cycles_per_mma = s / grid / iters / 16.0;
+  }
+  if (out) cudaFree(out);
+  if (e == cudaSuccess && st != 0) return -1;
+  return (int)e;
+}

@@ -5,7 +5,8 @@
 * FP32 FMA rate (the roofline denominator of the fp32 path), with operands that barely change and
   with operands that keep changing;
 * whether instructions mixed into a stream of packed FMAs cost issue slots;
-* how long one SM waits for a 32 / 64 KB TMA load out of L2 with one to three loads in flight.
+* how long one SM waits for a 32 / 64 KB TMA load out of L2 with one to three loads in flight;
+* SM cycles per tcgen05.mma (M = 128) in a long chain, by operand layout and N.
 """
 import ctypes
 import sys
@@ -20,6 +21,7 @@ def load():
     lib.opencnn_peaks_fp32_tflops_busy.argtypes = [ctypes.c_int, ctypes.c_int, d]
     lib.opencnn_peaks_issue_probe.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, d]
     lib.opencnn_peaks_tma_latency.argtypes = [ctypes.c_int] * 5 + [d]
+    lib.opencnn_peaks_mma_rate.argtypes = [ctypes.c_int] * 5 + [d]
     return lib
 
 
@@ -43,6 +45,16 @@ def tma_latency(lib, grid, iters=400):
             for b in (65536, 32768) for t in (1, 0) for d in (1, 2, 3)}
 
 
+MMA_LAYOUTS = ["MN-major, as the fused kernels hold them", "K-major, no swizzle", "K-major, 32-byte swizzle",
+               "K-major, 128-byte swizzle"]
+
+
+def mma_rate(lib, grid, iters=2000):
+    """{(kind, n, layout): cycles per MMA}; kind 0 BF16 (K = 16), 1 TF32 (K = 8)."""
+    return {(k, n, l): _call(lib.opencnn_peaks_mma_rate, k, n, l, iters, grid)
+            for k in (0, 1) for l in range(4) for n in (32, 64, 128, 256)}
+
+
 def main() -> int:
     import torch
     if not torch.cuda.is_available():
@@ -60,6 +72,10 @@ def main() -> int:
     for grid in (1, sms):
         for (b, t, d), cyc in tma_latency(lib, grid).items():
             print(f"{grid:3d} SMs  {b // 1024} KB {'tiled box ' if t else 'linear    '} {d} in flight: {cyc:6.0f} cycles per load, {b / cyc:5.1f} B/clk")
+    for (k, n, l), cyc in mma_rate(lib, sms).items():
+        macs = 128 * n * (16 if k == 0 else 8)
+        print(f"tcgen05.mma {'BF16' if k == 0 else 'TF32'} 128x{n:<3d} {MMA_LAYOUTS[l]:40s}: {cyc:6.1f} cycles per MMA, "
+              f"{macs / cyc:6.0f} MAC/clk")
     return 0
 
 

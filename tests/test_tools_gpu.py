@@ -81,3 +81,18 @@ def test_peak_probes_relations():
     for b in (65536, 32768):
         assert 300 < lat[(b, 1, 1)] < 5000, lat
         assert lat[(b, 1, 2)] <= 0.75 * lat[(b, 1, 1)], lat
+
+
+def test_mma_rate_probe_is_sane():
+    """The tcgen05.mma issue-rate probe: a chain of MMAs can never beat the tensor pipe (4096 BF16 / 2048 TF32
+    multiply-adds per clock and SM), and a wider MMA takes longer than a narrow one."""
+    from opencnn_b200 import peaks
+    lib = peaks.load()
+    r = peaks.mma_rate(lib, grid=8, iters=500)
+    for (kind, n, layout), cyc in r.items():
+        macs = 128 * n * (16 if kind == 0 else 8)
+        assert 1.0 < cyc < 5000.0, r
+        assert macs / cyc <= 1.05 * (4096 if kind == 0 else 2048), ((kind, n, layout), cyc)
+    for kind in (0, 1):
+        for layout in range(4):
+            assert r[(kind, 256, layout)] > r[(kind, 32, layout)], r
