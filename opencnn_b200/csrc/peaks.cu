@@ -274,20 +274,22 @@ struct MmaRateCfg {
 };
 constexpr uint32_t kRateABytes = 64 * 1024, kRateBBytes = 128 * 1024;
 
-// One thread per CTA issues `iters` groups of 16 MMAs (M = 128) on zero-filled shared memory, commits once and
-// waits; the other threads only clear shared memory.  Results are never read: only the issue-to-completion
-// time of the chain counts.  KIND 0 = kind::f16 (BF16, K = 16), 1 = kind::tf32 (K = 8).
-template <int KIND>
+// `issuers` threads of a CTA (lane 0 of warps 0 .. issuers-1) each issue `iters` groups of 16 / issuers MMAs
+// (M = 128, accumulators in disjoint TMEM columns) on zero-filled shared memory, commit once and wait; the other
+// threads only clear shared memory.  Results are never read: only the issue-to-completion time of the chains
+// counts (the slowest issuer's).  KIND 0 = kind::f16 (BF16, K = 16), 1 = kind::tf32 (K = 8).
+template <int KIND, int ISSUERS>
 __global__ void __launch_bounds__(128, 1) mma_rate_kernel(const MmaRateCfg cfg, int iters, long long *out, int *status) {
   extern __shared__ __align__(1024) uint8_t sm[];
   __shared__ uint32_t tmem_slot;
-  __shared__ __align__(8) uint64_t bar;
+  __shared__ __align__(8) uint64_t bar[4];
+  __shared__ long long took[4];
   __shared__ int dead;
   for (uint32_t i = threadIdx.x; i < (kRateABytes + kRateBBytes) / 16; i += blockDim.x)
     reinterpret_cast<uint4 *>(sm)[i] = make_uint4(0, 0, 0, 0);
   if (threadIdx.x == 0) {
     dead = 0;
-    ocb::mbar_init(ocb::smem_u32(&bar), 1);
+    for (int i = 0; i < 4; ++i) ocb::mbar_init(ocb::smem_u32(bar + i), 1);
     ocb::mbar_fence_init();
   }
   if (threadIdx.x < 32) ocb::tmem_alloc_512(ocb::smem_u32(&tmem_slot));
@@ -296,32 +298,41 @@ __global__ void __launch_bounds__(128, 1) mma_rate_kernel(const MmaRateCfg cfg, 
   __syncthreads();
   ocb::tc_fence_after();
   const uint32_t tmem = tmem_slot;
-  if (threadIdx.x == 0) {
+  const int warp = threadIdx.x >> 5;
+  if ((threadIdx.x & 31) == 0 && warp < ISSUERS) {
+    constexpr int kPer = 16 / ISSUERS;
     const uint32_t a0 = ocb::smem_u32(sm), b0 = a0 + kRateABytes;
-    uint64_t ad[16], bd[16];
+    uint64_t ad[kPer], bd[kPer];
+    uint32_t col[kPer];
 #pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      ad[j] = ocb::smem_desc(a0 + cfg.a_off[j], cfg.a_lbo, cfg.a_sbo, cfg.a_mode);
-      bd[j] = ocb::smem_desc(b0 + cfg.b_off[j], cfg.b_lbo, cfg.b_sbo, cfg.b_mode);
+    for (int j = 0; j < kPer; ++j) {
+      const int x = warp * kPer + j;
+      ad[j] = ocb::smem_desc(a0 + cfg.a_off[x], cfg.a_lbo, cfg.a_sbo, cfg.a_mode);
+      bd[j] = ocb::smem_desc(b0 + cfg.b_off[x], cfg.b_lbo, cfg.b_sbo, cfg.b_mode);
+      col[j] = tmem + ((uint32_t)x * cfg.n) % 512u;
     }
     const long long t0 = clock64();
     for (int it = 0; it < iters; ++it) {
 #pragma unroll
-      for (int j = 0; j < 16; ++j)
-        ocb::tc_mma<KIND>(tmem + ((uint32_t)j * cfg.n) % 512u, ad[j], bd[j], cfg.idesc, 1u);
+      for (int j = 0; j < kPer; ++j) ocb::tc_mma<KIND>(col[j], ad[j], bd[j], cfg.idesc, 1u);
     }
-    ocb::tc_commit(ocb::smem_u32(&bar));
-    ocb::mbar_wait(ocb::smem_u32(&bar), 0, &dead, status);
-    out[blockIdx.x] = clock64() - t0;
+    ocb::tc_commit(ocb::smem_u32(bar + warp));
+    ocb::mbar_wait(ocb::smem_u32(bar + warp), 0, &dead, status);
+    took[warp] = clock64() - t0;
   }
   ocb::tc_fence_before();
   __syncthreads();
+  if (threadIdx.x == 0) {
+    long long m = 0;
+    for (int i = 0; i < ISSUERS; ++i) m = took[i] > m ? took[i] : m;
+    out[blockIdx.x] = m;
+  }
   if (threadIdx.x < 32) ocb::tmem_dealloc_512(tmem);
 }
 }  // namespace
 
-// Average SM cycles per tcgen05.mma (cta_group::1, M = 128, fp32 accumulate) in a chain of 16 * iters MMAs issued
-// by one thread, over `grid` CTAs, one per SM.
+// Average SM cycles per tcgen05.mma (cta_group::1, M = 128, fp32 accumulate) when 16 * iters MMAs are issued by
+// `issuers` (1, 2 or 4) threads of a CTA, over `grid` CTAs, one per SM.
 //   kind    0 = BF16 (K = 16 per MMA), 1 = TF32 (K = 8)
 //   n       MMA N: 32, 64, 128 or 256
 //   layout  0 = both operands MN-major as the fused kernels hold them (A 128-byte swizzle, B 64-byte swizzle for
@@ -330,9 +341,9 @@ __global__ void __launch_bounds__(128, 1) mma_rate_kernel(const MmaRateCfg cfg, 
 //           2 = both K-major, 32-byte swizzle, rows of one K-step;
 //           3 = both K-major, 128-byte swizzle, rows of four K-steps (the usual GEMM operand layout).
 // Returns a cudaError_t code; -1 if a wait ran out.
-extern "C" int opencnn_peaks_mma_rate(int kind, int n, int layout, int iters, int grid, double *cycles_per_mma) {
+extern "C" int opencnn_peaks_mma_rate(int kind, int n, int layout, int issuers, int iters, int grid, double *cycles_per_mma) {
   if (!cycles_per_mma || kind < 0 || kind > 1 || (n != 32 && n != 64 && n != 128 && n != 256) || layout < 0 || layout > 3 ||
-      iters < 1 || grid < 1)
+      (issuers != 1 && issuers != 2 && issuers != 4) || iters < 1 || grid < 1)
     return (int)cudaErrorInvalidValue;
   MmaRateCfg c{};
   const uint32_t fmt = kind == 0 ? 1u : 2u, mn_major = layout == 0 ? 1u : 0u;
@@ -361,7 +372,8 @@ extern "C" int opencnn_peaks_mma_rate(int kind, int n, int layout, int iters, in
   for (uint32_t j = 0; j < 16; ++j) {
     c.a_off[j] = (j / kdiv) * a_tile + (j % kdiv) * kstep;
     c.b_off[j] = (j / kdiv) * b_tile + (j % kdiv) * kstep;
-    if (c.a_off[j] + a_tile > kRateABytes || c.b_off[j] + b_tile > kRateBBytes) return (int)cudaErrorInvalidValue;
+    // (a K-step offset stays inside its tile: the rows of a 128-byte-swizzle tile hold four K-steps)
+    if ((j / kdiv + 1) * a_tile > kRateABytes || (j / kdiv + 1) * b_tile > kRateBBytes) return (int)cudaErrorInvalidValue;
   }
   long long *out = nullptr;
   int *status = nullptr;
@@ -369,7 +381,10 @@ extern "C" int opencnn_peaks_mma_rate(int kind, int n, int layout, int iters, in
   if (e == cudaSuccess) e = cudaGetSymbolAddress(reinterpret_cast<void **>(&status), g_probe_status);
   if (e == cudaSuccess) e = cudaMemset(status, 0, sizeof(int));
   const size_t smem = kRateABytes + kRateBBytes;
-  auto kern = kind == 0 ? mma_rate_kernel<0> : mma_rate_kernel<1>;
+  using Kern = void (*)(const MmaRateCfg, int, long long *, int *);
+  const Kern kerns[2][3] = {{mma_rate_kernel<0, 1>, mma_rate_kernel<0, 2>, mma_rate_kernel<0, 4>},
+                            {mma_rate_kernel<1, 1>, mma_rate_kernel<1, 2>, mma_rate_kernel<1, 4>}};
+  const Kern kern = kerns[kind][issuers == 1 ? 0 : issuers == 2 ? 1 : 2];
   if (e == cudaSuccess) e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e == cudaSuccess) {
     for (int rep = 0; rep < 2; ++rep) kern<<<grid, 128, smem>>>(c, iters, out, status);

@@ -21,7 +21,7 @@ def load():
     lib.opencnn_peaks_fp32_tflops_busy.argtypes = [ctypes.c_int, ctypes.c_int, d]
     lib.opencnn_peaks_issue_probe.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, d]
     lib.opencnn_peaks_tma_latency.argtypes = [ctypes.c_int] * 5 + [d]
-    lib.opencnn_peaks_mma_rate.argtypes = [ctypes.c_int] * 5 + [d]
+    lib.opencnn_peaks_mma_rate.argtypes = [ctypes.c_int] * 6 + [d]
     return lib
 
 
@@ -50,9 +50,11 @@ MMA_LAYOUTS = ["MN-major, as the fused kernels hold them", "K-major, no swizzle"
 
 
 def mma_rate(lib, grid, iters=2000):
-    """{(kind, n, layout): cycles per MMA}; kind 0 BF16 (K = 16), 1 TF32 (K = 8)."""
-    return {(k, n, l): _call(lib.opencnn_peaks_mma_rate, k, n, l, iters, grid)
-            for k in (0, 1) for l in range(4) for n in (32, 64, 128, 256)}
+    """{(kind, n, layout, issuers): cycles per MMA}; kind 0 BF16 (K = 16), 1 TF32 (K = 8).  All layouts with one
+    issuing thread; the layout of the fused kernels also with two and four."""
+    cases = [(k, n, l, 1) for k in (0, 1) for l in range(4) for n in (32, 64, 128, 256)]
+    cases += [(k, n, 0, i) for k in (0, 1) for i in (2, 4) for n in (32, 64, 128)]
+    return {c: _call(lib.opencnn_peaks_mma_rate, c[0], c[1], c[2], c[3], iters, grid) for c in cases}
 
 
 def main() -> int:
@@ -72,10 +74,10 @@ def main() -> int:
     for grid in (1, sms):
         for (b, t, d), cyc in tma_latency(lib, grid).items():
             print(f"{grid:3d} SMs  {b // 1024} KB {'tiled box ' if t else 'linear    '} {d} in flight: {cyc:6.0f} cycles per load, {b / cyc:5.1f} B/clk")
-    for (k, n, l), cyc in mma_rate(lib, sms).items():
+    for (k, n, l, i), cyc in mma_rate(lib, sms).items():
         macs = 128 * n * (16 if k == 0 else 8)
-        print(f"tcgen05.mma {'BF16' if k == 0 else 'TF32'} 128x{n:<3d} {MMA_LAYOUTS[l]:40s}: {cyc:6.1f} cycles per MMA, "
-              f"{macs / cyc:6.0f} MAC/clk")
+        print(f"tcgen05.mma {'BF16' if k == 0 else 'TF32'} 128x{n:<3d} {MMA_LAYOUTS[l]:40s} {i} issuing thread(s): "
+              f"{cyc:6.1f} cycles per MMA, {macs / cyc:6.0f} MAC/clk")
     return 0
 
 

@@ -89,10 +89,10 @@ def test_mma_rate_probe_is_sane():
     from opencnn_b200 import peaks
     lib = peaks.load()
     r = peaks.mma_rate(lib, grid=8, iters=500)
-    for (kind, n, layout), cyc in r.items():
+    for (kind, n, layout, issuers), cyc in r.items():
         macs = 128 * n * (16 if kind == 0 else 8)
         assert 1.0 < cyc < 5000.0, r
-        assert macs / cyc <= 1.05 * (4096 if kind == 0 else 2048), ((kind, n, layout), cyc)
+        assert macs / cyc <= 1.05 * (4096 if kind == 0 else 2048), ((kind, n, layout, issuers), cyc)
     for kind in (0, 1):
         for layout in range(4):
-            assert r[(kind, 256, layout)] > r[(kind, 32, layout)], r
+            assert r[(kind, 256, layout, 1)] > r[(kind, 32, layout, 1)], r
