@@ -49,8 +49,8 @@ STACK = [(64, 56, 6), (128, 28, 8), (256, 14, 12), (512, 7, 6)]
 STACK_BATCH = 1024
 # dram__bytes_read.sum + dram__bytes_write.sum per wino_fp32_kernel launch, averaged over the four
 # layers of one step, from an ncu capture of this very command at full size.
-DRAM_TRAFFIC_PER_LAUNCH = 81.05e6
-DRAM_TRAFFIC_SOURCE = "ncu capture of `bench.py --steps 2 --warmup 3` (two 1-pass metrics, 8 launches), kernel as of the capture"
+DRAM_TRAFFIC_PER_LAUNCH = 79.89e6
+DRAM_TRAFFIC_SOURCE = "ncu capture of `bench.py --steps 2 --warmup 3 --no-extras` (two 1-pass metrics, 8 launches), kernel as of the capture"
 
 
 def direct_flops(N, C, K, HW):
