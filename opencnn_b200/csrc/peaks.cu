@@ -209,6 +209,27 @@ __global__ void __launch_bounds__(128, 1) tma_latency_kernel(const __grid_consta
 __device__ int g_probe_status = 0;
 }  // namespace
 
+// Tensor map of a BF16 transformed-filter workspace [C][16][K] with boxes {64 filters, 16 channels, 2 row blocks,
+// bytes / 4096 positions} and 128-byte swizzle.
+static cudaError_t make_workspace_map(CUtensorMap *map, void *ws, int C, int K, int bytes) {
+  void *fn = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  using Enc = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
+                           const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                           CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
+    return cudaErrorNotSupported;
+  cuuint64_t dims[4] = {64, (cuuint64_t)C, (cuuint64_t)K / 64, 16};
+  cuuint64_t strides[3] = {(cuuint64_t)16 * K * 2, 128, (cuuint64_t)K * 2};
+  cuuint32_t box[4] = {64, 16, 2, (cuuint32_t)(bytes / 4096)};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  if (reinterpret_cast<Enc>(fn)(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, ws, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return cudaErrorInvalidValue;
+  return cudaSuccess;
+}
+
 // Average cycles per load (issue to completion, `depth` loads in flight) over `grid` CTAs, one per SM.
 // bytes: 32768 or 65536; tiled: 1 = 4-D TMA box, 0 = linear bulk copy.  Returns a cudaError_t code.
 extern "C" int opencnn_peaks_tma_latency(int bytes, int tiled, int depth, int iters, int grid, double *cycles_per_load) {
@@ -224,25 +245,7 @@ extern "C" int opencnn_peaks_tma_latency(int bytes, int tiled, int depth, int it
   if (e == cudaSuccess) e = cudaMalloc(&out, (size_t)grid * sizeof(long long));
   if (e == cudaSuccess) e = cudaGetSymbolAddress(reinterpret_cast<void **>(&status), g_probe_status);
   CUtensorMap map;
-  if (e == cudaSuccess) {
-    void *fn = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    using Enc = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *, const cuuint64_t *,
-                             const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
-                             CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess)
-      e = cudaErrorNotSupported;
-    else {
-      cuuint64_t dims[4] = {64, (cuuint64_t)C, (cuuint64_t)K / 64, 16};
-      cuuint64_t strides[3] = {(cuuint64_t)16 * K * 2, 128, (cuuint64_t)K * 2};
-      cuuint32_t box[4] = {64, 16, 2, (cuuint32_t)(bytes / 4096)};
-      cuuint32_t estr[4] = {1, 1, 1, 1};
-      if (reinterpret_cast<Enc>(fn)(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, ws, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        e = cudaErrorInvalidValue;
-    }
-  }
+  if (e == cudaSuccess) e = make_workspace_map(&map, ws, C, K, bytes);
   const size_t smem = 3 * 65536 + 64;
   if (e == cudaSuccess) e = cudaFuncSetAttribute(tma_latency_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e == cudaSuccess) {
@@ -271,6 +274,7 @@ struct MmaRateCfg {
   uint32_t a_lbo, a_sbo, a_mode, b_lbo, b_sbo, b_mode;
   uint32_t a_off[16], b_off[16];   // byte offsets of the 16 operand tiles inside the A and B regions
   uint32_t n;                      // MMA N: accumulator j sits at TMEM column (j * n) % 512
+  uint32_t sync;                   // 1: commit and wait after every group (the round trip of a one-stage pipeline)
 };
 constexpr uint32_t kRateABytes = 64 * 1024, kRateBBytes = 128 * 1024;
 
@@ -315,9 +319,16 @@ __global__ void __launch_bounds__(128, 1) mma_rate_kernel(const MmaRateCfg cfg, 
     for (int it = 0; it < iters; ++it) {
 #pragma unroll
       for (int j = 0; j < kPer; ++j) ocb::tc_mma<KIND>(col[j], ad[j], bd[j], cfg.idesc, 1u);
+      if (cfg.sync) {
+        ocb::tc_commit(ocb::smem_u32(bar + warp));
+        if (!ocb::mbar_wait(ocb::smem_u32(bar + warp), (uint32_t)it & 1u, &dead, status)) break;
+        ocb::tc_fence_after();
+      }
     }
-    ocb::tc_commit(ocb::smem_u32(bar + warp));
-    ocb::mbar_wait(ocb::smem_u32(bar + warp), 0, &dead, status);
+    if (!cfg.sync) {
+      ocb::tc_commit(ocb::smem_u32(bar + warp));
+      ocb::mbar_wait(ocb::smem_u32(bar + warp), 0, &dead, status);
+    }
     took[warp] = clock64() - t0;
   }
   ocb::tc_fence_before();
@@ -340,8 +351,11 @@ __global__ void __launch_bounds__(128, 1) mma_rate_kernel(const MmaRateCfg cfg, 
 //           1 = both K-major, no swizzle (8 x 16-byte core matrices), rows of one K-step (32 bytes);
 //           2 = both K-major, 32-byte swizzle, rows of one K-step;
 //           3 = both K-major, 128-byte swizzle, rows of four K-steps (the usual GEMM operand layout).
+//   sync    0 = one commit at the end (the rate of the tensor pipe); 1 = every thread commits and waits after each
+//           of its groups of 16 / issuers MMAs: cycles per MMA then include the commit -> mbarrier -> wake-up
+//           round trip that a pipeline stage pays before it can be refilled.
 // Returns a cudaError_t code; -1 if a wait ran out.
-extern "C" int opencnn_peaks_mma_rate(int kind, int n, int layout, int issuers, int iters, int grid, double *cycles_per_mma) {
+static int mma_rate(int kind, int n, int layout, int issuers, int sync, int iters, int grid, double *cycles_per_mma) {
   if (!cycles_per_mma || kind < 0 || kind > 1 || (n != 32 && n != 64 && n != 128 && n != 256) || layout < 0 || layout > 3 ||
       (issuers != 1 && issuers != 2 && issuers != 4) || iters < 1 || grid < 1)
     return (int)cudaErrorInvalidValue;
@@ -349,6 +363,7 @@ extern "C" int opencnn_peaks_mma_rate(int kind, int n, int layout, int issuers, 
   const uint32_t fmt = kind == 0 ? 1u : 2u, mn_major = layout == 0 ? 1u : 0u;
   c.idesc = (1u << 4) | (fmt << 7) | (fmt << 10) | (mn_major << 15) | (mn_major << 16) | ((uint32_t)(n >> 3) << 17) | (8u << 24);
   c.n = (uint32_t)n;
+  c.sync = sync ? 1u : 0u;
   uint32_t a_tile, b_tile, kdiv = 1, kstep = 0;
   switch (layout) {
     case 0:
@@ -399,6 +414,137 @@ extern "C" int opencnn_peaks_mma_rate(int kind, int n, int layout, int issuers, 
     for (long long v : h) s += (double)v;
     *cycles_per_mma = s / grid / iters / 16.0;
   }
+  if (out) cudaFree(out);
+  if (e == cudaSuccess && st != 0) return -1;
+  return (int)e;
+}
+
+extern "C" int opencnn_peaks_mma_rate(int kind, int n, int layout, int issuers, int iters, int grid, double *cycles_per_mma) {
+  return mma_rate(kind, n, layout, issuers, 0, iters, grid, cycles_per_mma);
+}
+// Cycles per group of 16 / issuers MMAs (layout 0) when each issuing thread commits and waits after every group.
+extern "C" int opencnn_peaks_mma_round_trip(int kind, int n, int issuers, int iters, int grid, double *cycles_per_group) {
+  const int e = mma_rate(kind, n, 0, issuers, 1, iters, grid, cycles_per_group);
+  if (e == 0) *cycles_per_group *= 16.0;   // mma_rate divides by the 16 MMAs of a group
+  return e;
+}
+
+// ---- do TMA writes and MMA operand reads share the shared-memory bandwidth of an SM? -------------------------
+namespace {
+constexpr uint32_t kShareOperandBytes = 80 * 1024;   // 16 A tiles of 4 KB + 16 B tiles of 1 KB
+// Two threads issue `groups` groups of 8 MMAs each (BF16, 128 x 32 x 16, the operand layout of the fused kernels),
+// a third issues `loads` TMA loads of 64 KB with two in flight into a ring beside the operands.  Each role records
+// how long it took; a role with a count of 0 sits the run out.
+__global__ void __launch_bounds__(128, 1) smem_share_kernel(const __grid_constant__ CUtensorMap map, const MmaRateCfg cfg, int groups,
+                                                            int loads, int n_ci, long long *out, int *status) {
+  extern __shared__ __align__(1024) uint8_t sm[];
+  uint8_t *ring = sm + kShareOperandBytes;           // 80 KB is a multiple of 1024: the ring keeps the swizzle alignment
+  __shared__ uint32_t tmem_slot;
+  __shared__ __align__(8) uint64_t bar[4];
+  __shared__ long long took[3];
+  __shared__ int dead;
+  for (uint32_t i = threadIdx.x; i < kShareOperandBytes / 16; i += blockDim.x) reinterpret_cast<uint4 *>(sm)[i] = make_uint4(0, 0, 0, 0);
+  if (threadIdx.x == 0) {
+    dead = 0;
+    took[0] = took[1] = took[2] = 0;
+    for (int i = 0; i < 4; ++i) ocb::mbar_init(ocb::smem_u32(bar + i), 1);
+    ocb::mbar_fence_init();
+  }
+  if (threadIdx.x < 32) ocb::tmem_alloc_512(ocb::smem_u32(&tmem_slot));
+  ocb::fence_proxy_async_smem();
+  ocb::tc_fence_before();
+  __syncthreads();
+  ocb::tc_fence_after();
+  const uint32_t tmem = tmem_slot;
+  const int warp = threadIdx.x >> 5;
+  if ((threadIdx.x & 31) == 0) {
+    if (warp < 2 && groups > 0) {
+      const uint32_t a0 = ocb::smem_u32(sm), b0 = a0 + 64 * 1024;
+      uint64_t ad[8], bd[8];
+      uint32_t col[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int x = warp * 8 + j;
+        ad[j] = ocb::smem_desc(a0 + x * 4096, cfg.a_lbo, cfg.a_sbo, cfg.a_mode);
+        bd[j] = ocb::smem_desc(b0 + x * 1024, cfg.b_lbo, cfg.b_sbo, cfg.b_mode);
+        col[j] = tmem + (uint32_t)x * 32u;
+      }
+      const long long t0 = clock64();
+      for (int it = 0; it < groups; ++it) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) ocb::tc_mma<0>(col[j], ad[j], bd[j], cfg.idesc, 1u);
+      }
+      ocb::tc_commit(ocb::smem_u32(bar + warp));
+      ocb::mbar_wait(ocb::smem_u32(bar + warp), 0, &dead, status);
+      took[warp] = clock64() - t0;
+    } else if (warp == 2 && loads > 0) {
+      const long long t0 = clock64();
+      int issued = 0, waited = 0;
+      for (int it = 0; it < loads + 1; ++it) {
+        if (it < loads) {
+          const int s = it & 1;
+          const uint32_t b = ocb::smem_u32(bar + 2 + s);
+          ocb::mbar_arrive_expect_tx(b, 65536u);
+          ocb::tma_load_4d(ocb::smem_u32(ring + s * 65536), &map, b, 0, ((it * 7 + (int)blockIdx.x) % n_ci) * 16, 0, 0);
+          issued = it + 1;
+        }
+        const int w = it - 1;                        // two in flight: wait for the load before the one just issued
+        if (w >= 0) {
+          if (!ocb::mbar_wait(ocb::smem_u32(bar + 2 + (w & 1)), (uint32_t)(w >> 1) & 1u, &dead, status)) break;
+          waited = w + 1;
+        }
+      }
+      took[2] = clock64() - t0;
+      // after a wait that gave up: let what is still in flight land before the CTA exits
+      for (int w = waited; w < issued; ++w) ocb::mbar_wait_drain(ocb::smem_u32(bar + 2 + (w & 1)), (uint32_t)(w >> 1) & 1u);
+    }
+  }
+  ocb::tc_fence_before();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    out[3 * blockIdx.x + 0] = took[0] > took[1] ? took[0] : took[1];
+    out[3 * blockIdx.x + 1] = took[2];
+  }
+  if (threadIdx.x < 32) ocb::tmem_dealloc_512(tmem);
+}
+}  // namespace
+
+// Runs `groups` groups of 16 MMAs (two issuing threads) and `loads` 64 KB TMA loads (two in flight) at the same time
+// on each of `grid` SMs and returns the average cycles each side took.  Either count may be 0.
+extern "C" int opencnn_peaks_smem_share(int groups, int loads, int grid, double *mma_cycles, double *tma_cycles) {
+  if (!mma_cycles || !tma_cycles || groups < 0 || loads < 0 || grid < 1) return (int)cudaErrorInvalidValue;
+  const int C = 1024, K = 128;                                  // bf16 workspace of 4 MB: stays in L2
+  const size_t ws_bytes = (size_t)C * 16 * K * 2;
+  uint8_t *ws = nullptr;
+  long long *out = nullptr;
+  int *status = nullptr;
+  cudaError_t e = cudaMalloc(&ws, ws_bytes);
+  if (e == cudaSuccess) e = cudaMemset(ws, 0, ws_bytes);
+  if (e == cudaSuccess) e = cudaMalloc(&out, (size_t)grid * 3 * sizeof(long long));
+  if (e == cudaSuccess) e = cudaGetSymbolAddress(reinterpret_cast<void **>(&status), g_probe_status);
+  if (e == cudaSuccess) e = cudaMemset(status, 0, sizeof(int));
+  CUtensorMap map;
+  if (e == cudaSuccess) e = make_workspace_map(&map, ws, C, K, 65536);
+  MmaRateCfg c{};
+  c.idesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 15) | (1u << 16) | ((uint32_t)(32 >> 3) << 17) | (8u << 24);
+  c.a_lbo = 2048; c.a_sbo = 1024; c.a_mode = 2; c.b_lbo = 1024; c.b_sbo = 512; c.b_mode = 4;
+  const size_t smem = kShareOperandBytes + 2 * 65536;
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(smem_share_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e == cudaSuccess) {
+    for (int rep = 0; rep < 2; ++rep) smem_share_kernel<<<grid, 128, smem>>>(map, c, groups, loads, C / 16, out, status);
+    e = cudaDeviceSynchronize();
+  }
+  int st = 0;
+  if (e == cudaSuccess) e = cudaMemcpy(&st, status, sizeof(int), cudaMemcpyDeviceToHost);
+  if (e == cudaSuccess) {
+    std::vector<long long> h((size_t)grid * 3);
+    e = cudaMemcpy(h.data(), out, h.size() * sizeof(long long), cudaMemcpyDeviceToHost);
+    double a = 0.0, b = 0.0;
+    for (int i = 0; i < grid; ++i) { a += (double)h[3 * i]; b += (double)h[3 * i + 1]; }
+    *mma_cycles = a / grid;
+    *tma_cycles = b / grid;
+  }
+  if (ws) cudaFree(ws);
   if (out) cudaFree(out);
   if (e == cudaSuccess && st != 0) return -1;
   return (int)e;

@@ -256,7 +256,8 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
   uint8_t *v_s = u_s + kTcStages * Cfg::kUBytes;                       // [stage][16 xi][...]  1 KB per position
   uint64_t *bars = reinterpret_cast<uint64_t *>(v_s + kTcStages * kTcVBytes);
   uint64_t *raw_full = bars, *raw_empty = bars + SR, *u_full = bars + 2 * SR, *uv_empty = u_full + 4;   // u_full: U landed and V written
-  uint64_t *acc_full = u_full + 6, *acc_empty = u_full + 7;
+  uint64_t *acc_full = u_full + 6;
+  uint64_t *acc_empty = u_full + 14;                   // [4]: one per column of the 4x4 positions (see the epilogue)
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(u_full + 8);
   volatile int *dead = reinterpret_cast<volatile int *>(u_full + 9);
   uint64_t *mma_done = u_full + 10;                    // one per MMA-issuing thread: "all my MMAs have completed"
@@ -277,7 +278,7 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
       mbar_init(smem_u32(uv_empty + s), Cfg::kIssuers);      // one tcgen05.commit per MMA-issuing thread
     }
     mbar_init(smem_u32(acc_full), Cfg::kIssuers);
-    mbar_init(smem_u32(acc_empty), kTcEpilogueWarps);
+    for (int j = 0; j < 4; ++j) mbar_init(smem_u32(acc_empty + j), kTcEpilogueWarps);
     for (int i = 0; i < Cfg::kIssuers; ++i) mbar_init(smem_u32(mma_done + i), 1);
     mbar_fence_init();
   }
@@ -362,8 +363,12 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
     // loop: building them per instruction made each of these small MMAs (N = 32 occupies the
     // tensor pipe ~50 cycles) cost ~180 cycles.
     if (lane == 0) {
+      // A thread issues whole columns of the 4x4 positions (two columns in BF16, one in TF32), column by column:
+      // the epilogue hands the accumulators back per column, so the next tile's first MMAs start while the
+      // other columns are still being read.
       constexpr int kPer = 16 / Cfg::kIssuers;                              // positions per issuing thread
-      const int x0 = warp == kTcMmaWarp ? 0 : kPer * (warp - kTcMmaWarpB + 1);   // first position of this thread
+      const int me = warp == kTcMmaWarp ? 0 : warp - kTcMmaWarpB + 1;
+      const int col0 = me * (kPer / 4);                                     // first column of this thread
       const uint32_t idesc = instr_desc<DT>();
       // A: 128 filters x KC channels, filter-contiguous rows of 128 B (64 bf16 / 32 tf32 filters), 8-channel
       //    groups 1 KB apart, 128-byte-row blocks of the filter axis KC*128 B apart.
@@ -382,15 +387,21 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
         const uint32_t use = g / kTcStages;
         // A wait that gave up: stop issuing (the operands or the accumulators are not ready).
         if (!mbar_wait(smem_u32(u_full + s), use & 1, dead, p.status)) break;      // U landed and V written
-        if (ci == 0 && seq > 0 && !mbar_wait(smem_u32(acc_empty), (seq - 1) & 1, dead, p.status)) break;   // TMEM drained
         tc_fence_after();
-        const uint64_t ad = ((dup || HU) ? a_desc0_dup : a_desc0) + (uint64_t)(s * (Cfg::kUBytes >> 4)), bd = b_desc0 + (uint64_t)(s * (kTcVBytes >> 4));
-        const uint32_t accumulate = ci > 0 ? 1u : 0u;
+        const uint64_t ad = ((dup || HU) ? a_desc0_dup : a_desc0) + (uint64_t)(s * (Cfg::kUBytes >> 4)) + (uint64_t)(col0 * (Cfg::kUPosBytes >> 4)),
+                       bd = b_desc0 + (uint64_t)(s * (kTcVBytes >> 4)) + (uint64_t)(col0 * (1024 >> 4));
+        const uint32_t accumulate = ci > 0 ? 1u : 0u, d0 = tmem_base + col0 * kTcN;
+        bool ok = true;
 #pragma unroll
         for (int xo = 0; xo < kPer; ++xo) {
-          const int xi = x0 + xo;
-          tc_mma<DT>(tmem_base + xi * kTcN, ad + (uint64_t)(xi * (Cfg::kUPosBytes >> 4)), bd + (uint64_t)(xi * (1024 >> 4)), idesc, accumulate);
+          const int xr = 4 * (xo & 3) + (xo >> 2);                          // position relative to col0: row xo & 3, column xo >> 2
+          if ((xo & 3) == 0 && ci == 0 && seq > 0) {                         // first write to a column of a new tile: drained?
+            if (!mbar_wait(smem_u32(acc_empty + col0 + (xo >> 2)), (seq - 1) & 1, dead, p.status)) { ok = false; break; }
+            tc_fence_after();
+          }
+          tc_mma<DT>(d0 + xr * kTcN, ad + (uint64_t)(xr * (Cfg::kUPosBytes >> 4)), bd + (uint64_t)(xr * (1024 >> 4)), idesc, accumulate);
         }
+        if (!ok) break;
         tc_commit(smem_u32(uv_empty + s));                 // stage reusable when these MMAs are done
         if (++ci == cpt) {
           tc_commit(smem_u32(acc_full));                   // tile finished
@@ -401,7 +412,6 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
       }
       // Tensor memory is freed at the end of the kernel: every MMA this thread issued must have
       // completed by then, also after a give-up (then nobody waited for acc_full).
-      const int me = warp == kTcMmaWarp ? 0 : warp - kTcMmaWarpB + 1;
       tc_commit(smem_u32(mma_done + me));
       mbar_wait_drain(smem_u32(mma_done + me), 0);
     }
@@ -429,56 +439,83 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
       const uint32_t tlane = tmem_base + ((uint32_t)(quarter * 32) << 16);
       // Warps whose 32 filters all lie beyond K (K = 64 layers) have nothing to read or store.
       const bool warp_valid = (tc.kb * kTcM + fq * 32) < p.K;
-      // this warp's share of the 32 images: image quads jbase .. jbase + iters - 1
-      const int iters = dup ? 2 : 4;
+      // this warp's share of the 32 images: image quads jbase .. jbase + nq - 1
+      const int nq = dup ? 2 : 4;
       const int jbase = dup ? 2 * (2 * (quarter >> 1) + sub) : 4 * sub;
-      bool released = false;
-#pragma unroll 1
-      for (int jj = 0; jj < iters; jj += 2) {
-        if (!warp_valid) break;
-        // Two image quads per step so that every store is one full 32-byte sector per lane: lanes
-        // are filters, i.e. different output rows, and 16-byte stores would touch twice the sectors.
-        float yq[2][4][4];                      // [quad][output position][image]
+      // Y = A^T M A column by column of the 4x4 positions: column j (positions j, 4+j, 8+j, 12+j) gives the two
+      // row sums a[j], a[4+j] of output_transform, which are folded into the four outputs at once - the same
+      // operations in the same order.  After a column has been read it is handed back (acc_empty[j]), so the
+      // MMAs of the next tile into those four accumulators overlap the rest of this epilogue.
+      float y[4][4][4];                         // [image quad][output position][image]
 #pragma unroll
-        for (int h2 = 0; h2 < 2; ++h2) {
-          const int j = jbase + jj + h2;
-          float mm[16][4];
+      for (int j = 0; j < 4; ++j) {
 #pragma unroll
-          for (int xi = 0; xi < 16; ++xi) tmem_ld_x4(tlane + xi * kTcN + 4 * j, mm[xi]);
-          tmem_ld_wait();
-          if (h2 == 1 && jj + 2 >= iters) {
-            // That was this warp's last read of the accumulators: hand them back before the
-            // arithmetic and the stores of the last step, so the next tile's MMAs start earlier.
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(acc_empty));
-            released = true;
-          }
+        for (int h = 0; h < 2; ++h) {
+          if (warp_valid && 2 * h < nq) {
+            float mm[2][4][4];                  // [quad of this half][row][image]
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            float col[16], yy[4];
+            for (int q2 = 0; q2 < 2; ++q2)
 #pragma unroll
-            for (int xi = 0; xi < 16; ++xi) col[xi] = mm[xi][e];
-            output_transform(col, yy);
+              for (int r = 0; r < 4; ++r) tmem_ld_x4(tlane + (4 * r + j) * kTcN + 4 * (jbase + 2 * h + q2), mm[q2][r]);
+            tmem_ld_wait();
 #pragma unroll
-            for (int q = 0; q < 4; ++q) yq[h2][q][e] = yy[q];
-          }
-        }
-        // eight images per lane and step; N is a multiple of 8, so a step is inside N or outside
-        if (valid && tc.nb * kTcN + 4 * (jbase + jj) < p.N) {
-          float *dst = ybase + 4 * (jbase + jj);
-          st_global_v8(dst, yq[0][0], yq[1][0]);
-          if (col1) st_global_v8(dst + dW, yq[0][1], yq[1][1]);
-          if (row1) {
-            st_global_v8(dst + dH, yq[0][2], yq[1][2]);
-            if (col1) st_global_v8(dst + dH + dW, yq[0][3], yq[1][3]);
+            for (int q2 = 0; q2 < 2; ++q2)
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float lo = __fadd_rn(__fadd_rn(mm[q2][0][e], mm[q2][1][e]), mm[q2][2][e]);
+                const float hi = __fsub_rn(__fsub_rn(mm[q2][1][e], mm[q2][2][e]), mm[q2][3][e]);
+                float(&yy)[4][4] = y[2 * h + q2];
+                if (j == 0) { yy[0][e] = lo; yy[2][e] = hi; }
+                if (j == 1) { yy[0][e] = __fadd_rn(yy[0][e], lo); yy[1][e] = lo; yy[2][e] = __fadd_rn(yy[2][e], hi); yy[3][e] = hi; }
+                if (j == 2) { yy[0][e] = __fadd_rn(yy[0][e], lo); yy[1][e] = __fsub_rn(yy[1][e], lo);
+                              yy[2][e] = __fadd_rn(yy[2][e], hi); yy[3][e] = __fsub_rn(yy[3][e], hi); }
+                if (j == 3) { yy[1][e] = __fsub_rn(yy[1][e], lo); yy[3][e] = __fsub_rn(yy[3][e], hi); }
+              }
           }
         }
-      }
-      if (!released) {                       // warps without valid filters
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(acc_empty));
+        if (lane == 0) mbar_arrive(smem_u32(acc_empty + j));
+      }
+      // Stores.  Lanes are filters, i.e. different output rows, so a warp-wide store touches 32 lines however it
+      // is arranged; what can be halved is the number of lines per byte.  A lane holds 16 consecutive images
+      // (64 bytes) of its filter per output position: neighbouring lanes swap halves, so that one instruction
+      // writes the 64 bytes of the pair's even filter (32 bytes per lane) and the next those of the odd filter -
+      // 16 lines of two full sectors per instruction instead of 32 lines of one.  (Measured on the 56x56 layer:
+      // 7 % of the kernel; the memory pipe is shared with the transform warps' shared-memory traffic.)
+      if (warp_valid) {
+        if (nq == 4) {
+          const bool odd = (lane & 1) != 0;
+          float *pair_base = ybase - (odd ? plane : 0) + 16 * sub + (odd ? 8 : 0);   // even filter of the pair, this lane's half
+          const bool n_ok = tc.nb * kTcN + 16 * sub + (odd ? 8 : 0) < p.N;         // N is a multiple of 8
+          const bool ok_even = n_ok && (k - (odd ? 1 : 0)) < p.K, ok_odd = n_ok && (k + (odd ? 0 : 1)) < p.K;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            float ev[2][4], od[2][4];           // this lane's half of the even / odd filter's 64 bytes
+#pragma unroll
+            for (int q2 = 0; q2 < 2; ++q2)
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float lo = y[q2][q][e], hi = y[2 + q2][q][e];              // images 0-7 / 8-15 of this lane's filter
+                const float got = __shfl_xor_sync(0xFFFFFFFFu, odd ? lo : hi, 1);
+                ev[q2][e] = odd ? got : lo;
+                od[q2][e] = odd ? hi : got;
+              }
+            const bool here = (q == 0) || (q == 1 && col1) || (q == 2 && row1) || (q == 3 && row1 && col1);
+            float *dst = pair_base + ((q & 1) ? dW : 0) + ((q & 2) ? dH : 0);
+            if (here && ok_even) st_global_v8(dst, ev[0], ev[1]);
+            if (here && ok_odd) st_global_v8(dst + plane, od[0], od[1]);
+          }
+        } else if (valid && tc.nb * kTcN + 4 * jbase < p.N) {
+          // eight images per lane (repeated-filter tiles): one full 32-byte sector per lane and store
+          float *dst = ybase + 4 * jbase;
+          st_global_v8(dst, y[0][0], y[1][0]);
+          if (col1) st_global_v8(dst + dW, y[0][1], y[1][1]);
+          if (row1) {
+            st_global_v8(dst + dH, y[0][2], y[1][2]);
+            if (col1) st_global_v8(dst + dH + dW, y[0][3], y[1][3]);
+          }
+        }
       }
     }
   }

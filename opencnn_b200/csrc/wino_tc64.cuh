@@ -51,7 +51,8 @@ wino_tc64_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constan
   uint64_t *bars = reinterpret_cast<uint64_t *>(zero_hi + kT64ZeroBytes);
   uint64_t *raw_full = bars, *raw_empty = raw_full + SR, *u_full = raw_empty + SR, *u_empty = u_full + SU,
            *v_ready = u_empty + SU, *v_empty = v_ready + SV;
-  uint64_t *acc_full = v_empty + SV, *acc_empty = acc_full + 1, *mma_done = acc_full + 2;   // mma_done[2]
+  uint64_t *acc_full = v_empty + SV, *mma_done = acc_full + 2;   // mma_done[2]
+  uint64_t *acc_empty = acc_full + 6;                  // [4]: one per column of the 4x4 positions
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_full + 4);
   volatile int *dead = reinterpret_cast<volatile int *>(acc_full + 5);
 
@@ -83,7 +84,7 @@ wino_tc64_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constan
       mbar_init(smem_u32(v_empty + s), 2);
     }
     mbar_init(smem_u32(acc_full), 2);
-    mbar_init(smem_u32(acc_empty), kTcEpilogueWarps);
+    for (int j = 0; j < 4; ++j) mbar_init(smem_u32(acc_empty + j), kTcEpilogueWarps);
     mbar_init(smem_u32(mma_done + 0), 1);
     mbar_init(smem_u32(mma_done + 1), 1);
     mbar_fence_init();
@@ -147,10 +148,10 @@ wino_tc64_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constan
       }
     }
   } else if (warp == kTcMmaWarp || warp == kTcMmaWarpB) {
-    // ===================================== MMA issuers (two threads, eight positions each) ======
+    // ===================================== MMA issuers (two threads, two position columns each) ==
     if (lane == 0) {
       const int me = warp == kTcMmaWarp ? 0 : 1;
-      const int x0 = 8 * me;
+      const int col0 = 2 * me;                         // columns col0, col0 + 1 of the 4x4 positions, column by column
       const uint32_t idesc = instr_desc<kTcBf16>();
       // A blocks: 64 filters x 16 channels, filter-contiguous rows of 128 B (128-byte swizzle), 8-channel groups 1 KB
       // apart; the second block lies `lbo` bytes after the first.  Per position the U block moves by 2 KB, so
@@ -169,17 +170,22 @@ wino_tc64_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constan
         // A wait that gave up: stop issuing (the operands or the accumulators are not ready).
         if (b == 0 && !mbar_wait(smem_u32(u_full + su), ((g >> 1) / SU) & 1, dead, p.status)) break;
         if (!mbar_wait(smem_u32(v_ready + sv), (g / SV) & 1, dead, p.status)) break;
-        if (b == 0 && ci == 0 && seq > 0 && !mbar_wait(smem_u32(acc_empty), (seq - 1) & 1, dead, p.status)) break;   // TMEM drained
         tc_fence_after();
-        const uint64_t ad = b == 0 ? a_top0 + (uint64_t)su * (kStageStart - kStageLbo) : a_bot0 + (uint64_t)su * kStageLbo;
         const uint64_t astep = b == 0 ? kPosStart - kPosLbo : kPosLbo;
-        const uint64_t bd = b_desc0 + (uint64_t)(sv * (kTcVBytes >> 4));
-        const uint32_t accumulate = (ci > 0 || b > 0) ? 1u : 0u;
+        const uint64_t ad = (b == 0 ? a_top0 + (uint64_t)su * (kStageStart - kStageLbo) : a_bot0 + (uint64_t)su * kStageLbo) + (uint64_t)col0 * astep;
+        const uint64_t bd = b_desc0 + (uint64_t)(sv * (kTcVBytes >> 4)) + (uint64_t)(col0 * (1024 >> 4));
+        const uint32_t accumulate = (ci > 0 || b > 0) ? 1u : 0u, d0 = tmem_base + col0 * kTcN;
+        bool ok = true;
 #pragma unroll
         for (int xo = 0; xo < 8; ++xo) {
-          const int xi = x0 + xo;
-          tc_mma<kTcBf16>(tmem_base + xi * kTcN, ad + (uint64_t)xi * astep, bd + (uint64_t)(xi * (1024 >> 4)), idesc, accumulate);
+          const int xr = 4 * (xo & 3) + (xo >> 2);     // position relative to col0: row xo & 3, column xo >> 2
+          if ((xo & 3) == 0 && b == 0 && ci == 0 && seq > 0) {   // first write to a column of a new tile: drained?
+            if (!mbar_wait(smem_u32(acc_empty + col0 + (xo >> 2)), (seq - 1) & 1, dead, p.status)) { ok = false; break; }
+            tc_fence_after();
+          }
+          tc_mma<kTcBf16>(d0 + xr * kTcN, ad + (uint64_t)xr * astep, bd + (uint64_t)(xr * (1024 >> 4)), idesc, accumulate);
         }
+        if (!ok) break;
         tc_commit(smem_u32(v_empty + sv));                 // V stage reusable when these MMAs are done
         if (b == 1) {
           tc_commit(smem_u32(u_empty + su));               // and the filter slice after the second image block
@@ -200,7 +206,6 @@ wino_tc64_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constan
     const int sub = (warp - kTcFirstEpilogueWarp) >> 2;                  // 0 / 1: which 16 of the block's 32 images
     const int fq = quarter & 1, ib = quarter >> 1;                       // filters 32*fq .. +31 of image block ib
     const int k = fq * 32 + lane;
-    const bool kvalid = k < p.K;
     const bool warp_valid = fq * 32 < p.K;
     const size_t plane = (size_t)p.H * p.W * p.N;
     const size_t dW = (size_t)p.N, dH = (size_t)p.W * p.N;
@@ -214,49 +219,66 @@ wino_tc64_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constan
       const bool row1 = (oh0 + 1) < p.H, col1 = (ow0 + 1) < p.W;
       float *ybase = p.y + (size_t)k * plane + ((size_t)oh0 * p.W + ow0) * p.N + (size_t)nb * kTcN + 16 * sub;
       const bool active = warp_valid && nb < p.n_blocks;
-      float yq[2][4][4];                                                 // [quad][output position][image]
-      if (active) {
-#pragma unroll 1
-        for (int step = 0; step < 2; ++step) {
-          // two image quads per step so that every store is one full 32-byte sector per lane
+      // Y = A^T M A column by column of the 4x4 positions: column j (positions j, 4+j, 8+j, 12+j) gives the two
+      // row sums a[j], a[4+j] of output_transform, which are folded into the four outputs at once - the same
+      // operations in the same order.  After a column has been read it is handed back (acc_empty[j]), so the
+      // MMAs of the next tile into those four accumulators overlap the rest of this epilogue.
+      float y[4][4][4];                                                  // [image quad][output position][image]
 #pragma unroll
-          for (int h2 = 0; h2 < 2; ++h2) {
-            const int col = 16 * sub + 8 * step + 4 * h2;
-            float mm[16][4];
+      for (int j = 0; j < 4; ++j) {
 #pragma unroll
-            for (int xi = 0; xi < 16; ++xi) tmem_ld_x4(tlane + xi * kTcN + col, mm[xi]);
+        for (int h = 0; h < 2; ++h) {
+          if (active) {
+            float mm[2][4][4];                                           // [quad of this half][row][image]
+#pragma unroll
+            for (int q2 = 0; q2 < 2; ++q2)
+#pragma unroll
+              for (int r = 0; r < 4; ++r) tmem_ld_x4(tlane + (4 * r + j) * kTcN + 16 * sub + 8 * h + 4 * q2, mm[q2][r]);
             tmem_ld_wait();
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              float colv[16], yy[4];
+            for (int q2 = 0; q2 < 2; ++q2)
 #pragma unroll
-              for (int xi = 0; xi < 16; ++xi) colv[xi] = mm[xi][e];
-              output_transform(colv, yy);
-#pragma unroll
-              for (int q = 0; q < 4; ++q) yq[h2][q][e] = yy[q];
-            }
-          }
-          if (step == 1) {
-            // that was this warp's last read of the accumulators: hand them back before the last stores
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(acc_empty));
-          }
-          // eight images per lane and step; N is a multiple of 8, so a step is inside N or outside
-          if (kvalid && nb * kTcN + 16 * sub + 8 * step < p.N) {
-            float *dst = ybase + 8 * step;
-            st_global_v8(dst, yq[0][0], yq[1][0]);
-            if (col1) st_global_v8(dst + dW, yq[0][1], yq[1][1]);
-            if (row1) {
-              st_global_v8(dst + dH, yq[0][2], yq[1][2]);
-              if (col1) st_global_v8(dst + dH + dW, yq[0][3], yq[1][3]);
-            }
+              for (int e = 0; e < 4; ++e) {
+                const float lo = __fadd_rn(__fadd_rn(mm[q2][0][e], mm[q2][1][e]), mm[q2][2][e]);
+                const float hi = __fsub_rn(__fsub_rn(mm[q2][1][e], mm[q2][2][e]), mm[q2][3][e]);
+                float(&yy)[4][4] = y[2 * h + q2];
+                if (j == 0) { yy[0][e] = lo; yy[2][e] = hi; }
+                if (j == 1) { yy[0][e] = __fadd_rn(yy[0][e], lo); yy[1][e] = lo; yy[2][e] = __fadd_rn(yy[2][e], hi); yy[3][e] = hi; }
+                if (j == 2) { yy[0][e] = __fadd_rn(yy[0][e], lo); yy[1][e] = __fsub_rn(yy[1][e], lo);
+                              yy[2][e] = __fadd_rn(yy[2][e], hi); yy[3][e] = __fsub_rn(yy[3][e], hi); }
+                if (j == 3) { yy[1][e] = __fsub_rn(yy[1][e], lo); yy[3][e] = __fsub_rn(yy[3][e], hi); }
+              }
           }
         }
-      } else {                                 // nothing to read or store: only hand the accumulators back
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(acc_empty));
+        if (lane == 0) mbar_arrive(smem_u32(acc_empty + j));
+      }
+      // Stores: neighbouring lanes (filters) swap halves of their 16 images, so that one instruction writes the
+      // 64 bytes of the pair's even filter (32 bytes per lane) and the next those of the odd filter - 16 lines of
+      // two full sectors per instruction instead of 32 lines of one (see wino_tc_kernel).
+      if (active) {
+        const bool odd = (lane & 1) != 0;
+        float *pair_base = ybase - (odd ? plane : 0) + (odd ? 8 : 0);           // even filter of the pair, this lane's half
+        const bool n_ok = nb * kTcN + 16 * sub + (odd ? 8 : 0) < p.N;            // N is a multiple of 8
+        const bool ok_even = n_ok && (k - (odd ? 1 : 0)) < p.K, ok_odd = n_ok && (k + (odd ? 0 : 1)) < p.K;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          float ev[2][4], od[2][4];             // this lane's half of the even / odd filter's 64 bytes
+#pragma unroll
+          for (int q2 = 0; q2 < 2; ++q2)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float lo = y[q2][q][e], hi = y[2 + q2][q][e];                // images 0-7 / 8-15 of this lane's filter
+              const float got = __shfl_xor_sync(0xFFFFFFFFu, odd ? lo : hi, 1);
+              ev[q2][e] = odd ? got : lo;
+              od[q2][e] = odd ? hi : got;
+            }
+          const bool here = (q == 0) || (q == 1 && col1) || (q == 2 && row1) || (q == 3 && row1 && col1);
+          float *dst = pair_base + ((q & 1) ? dW : 0) + ((q & 2) ? dH : 0);
+          if (here && ok_even) st_global_v8(dst, ev[0], ev[1]);
+          if (here && ok_odd) st_global_v8(dst + plane, od[0], od[1]);
+        }
       }
     }
   }

@@ -6,7 +6,8 @@
   with operands that keep changing;
 * whether instructions mixed into a stream of packed FMAs cost issue slots;
 * how long one SM waits for a 32 / 64 KB TMA load out of L2 with one to three loads in flight;
-* SM cycles per tcgen05.mma (M = 128) in a long chain, by operand layout and N.
+* SM cycles per tcgen05.mma (M = 128) in a long chain, by operand layout, N and issuing threads; the
+  commit -> wait round trip; whether MMA operand reads and TMA writes share an SM's shared-memory bandwidth.
 """
 import ctypes
 import sys
@@ -22,6 +23,8 @@ def load():
     lib.opencnn_peaks_issue_probe.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, d]
     lib.opencnn_peaks_tma_latency.argtypes = [ctypes.c_int] * 5 + [d]
     lib.opencnn_peaks_mma_rate.argtypes = [ctypes.c_int] * 6 + [d]
+    lib.opencnn_peaks_mma_round_trip.argtypes = [ctypes.c_int] * 5 + [d]
+    lib.opencnn_peaks_smem_share.argtypes = [ctypes.c_int] * 3 + [d, d]
     return lib
 
 
@@ -57,6 +60,24 @@ def mma_rate(lib, grid, iters=2000):
     return {c: _call(lib.opencnn_peaks_mma_rate, c[0], c[1], c[2], c[3], iters, grid) for c in cases}
 
 
+def mma_round_trip(lib, grid, iters=2000):
+    """{(kind, issuers): cycles from the first MMA of a group of 16 / issuers (N = 32) to the wake-up after its commit}."""
+    return {(k, i): _call(lib.opencnn_peaks_mma_round_trip, k, 32, i, iters, grid) for k in (0, 1) for i in (1, 2, 4)}
+
+
+def smem_share(lib, grid, groups=2000, loads=1600):
+    """MMA operand reads (80 KB per group of 16 MMAs) and TMA writes (64 KB per load) alone and together:
+    {"mma alone" | "tma alone" | "together": (mma cycles, tma cycles)}."""
+    out = {}
+    for name, g, l in (("mma alone", groups, 0), ("tma alone", 0, loads), ("together", groups, loads)):
+        a, b = ctypes.c_double(0.0), ctypes.c_double(0.0)
+        err = lib.opencnn_peaks_smem_share(g, l, grid, ctypes.byref(a), ctypes.byref(b))
+        if err != 0:
+            raise RuntimeError(f"opencnn_peaks_smem_share({g}, {l}, {grid}) returned {err}")
+        out[name] = (a.value, b.value)
+    return out
+
+
 def main() -> int:
     import torch
     if not torch.cuda.is_available():
@@ -78,6 +99,15 @@ def main() -> int:
         macs = 128 * n * (16 if k == 0 else 8)
         print(f"tcgen05.mma {'BF16' if k == 0 else 'TF32'} 128x{n:<3d} {MMA_LAYOUTS[l]:40s} {i} issuing thread(s): "
               f"{cyc:6.1f} cycles per MMA, {macs / cyc:6.0f} MAC/clk")
+    for (k, i), cyc in mma_round_trip(lib, sms).items():
+        print(f"{'BF16' if k == 0 else 'TF32'} {16 // i:2d} MMAs 128x32 per thread, {i} thread(s), commit + wait after each group: "
+              f"{cyc:6.0f} cycles per group")
+    groups, loads = 2000, 1600
+    for grid in (1, sms):
+        for name, (a, b) in smem_share(lib, grid, groups, loads).items():
+            mma = f"MMA operand reads {groups * 80 * 1024 / a:6.1f} B/clk" if a else "no MMAs"
+            tma = f"TMA writes {loads * 65536 / b:6.1f} B/clk" if b else "no loads"
+            print(f"{grid:3d} SMs  {name:10s}: {mma:32s} {tma}")
     return 0
 
 

@@ -96,3 +96,7 @@ def test_mma_rate_probe_is_sane():
     for kind in (0, 1):
         for layout in range(4):
             assert r[(kind, 256, layout, 1)] > r[(kind, 32, layout, 1)], r
+    trip = peaks.mma_round_trip(lib, grid=8, iters=300)
+    for (kind, issuers), cyc in trip.items():
+        # a group that is committed and waited for cannot be faster than its MMAs in the pipe
+        assert cyc >= 0.95 * (16 // issuers) * r[(kind, 32, 0, 1 if issuers == 1 else issuers)] and cyc < 20000.0, trip
