@@ -83,8 +83,8 @@ enum opencnn_tc_kernel {
   OPENCNN_TC_AUTO = 0,          /* what opencnn_winograd_forward would take */
   OPENCNN_TC_SINGLE_CTA = 1,    /* one CTA per tile of 128 filters x 32 images, all 16 Winograd positions */
   OPENCNN_TC_PAIR_LOCAL = 2,    /* CTA pair per 128 x 64 tile, positions split 8 / 8, each CTA transforms all 64 images */
-  OPENCNN_TC_STACKED_BLOCKS = 3 /* OPENCNN_BF16 with filt_k <= 64 only: one CTA per 64 filters x 64 images, the two
-                                   32-image blocks in the two halves of the accumulator rows */
+  OPENCNN_TC_STACKED_BLOCKS = 3 /* filt_k <= 64 only: one CTA per 64 filters x 64 images, the two 32-image blocks in
+                                   the two halves of the accumulator rows */
 };
 int opencnn_winograd_forward_kernel(const float *input, const float *workspace, float *output, int in_n,
                                     int in_c, int in_h, int in_w, int filt_k, int precision, int kernel,

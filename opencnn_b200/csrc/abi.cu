@@ -124,7 +124,11 @@ cudaError_t device_state(DeviceState **out) {
       }
     }
     if (err == cudaSuccess)
-      err = cudaFuncSetAttribute(ocb::wino_tc64_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ocb::kT64SmemBytes);
+      err = cudaFuncSetAttribute(ocb::wino_tc64_kernel<ocb::kTcBf16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)ocb::T64Cfg<ocb::kTcBf16>::kSmemBytes);
+    if (err == cudaSuccess)
+      err = cudaFuncSetAttribute(ocb::wino_tc64_kernel<ocb::kTcTf32>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 (int)ocb::T64Cfg<ocb::kTcTf32>::kSmemBytes);
     if (err == cudaSuccess) err = cudaGetSymbolAddress(reinterpret_cast<void **>(&st.status_ptr), g_status);
     st.init_error = err;
   });
@@ -355,7 +359,8 @@ cudaError_t launch_wino_tc2(const float *input, const float *workspace, float *o
   return cudaGetLastError();
 }
 
-// BF16 layers with at most 64 filters: two 32-image blocks share the 128 accumulator rows (wino_tc64.cuh).
+// Layers with at most 64 filters: two 32-image blocks share the 128 accumulator rows (wino_tc64.cuh).
+template <int DT>
 cudaError_t launch_wino_tc64(const float *input, const float *workspace, float *output, int N, int C, int H, int W,
                              int K, cudaStream_t stream) {
   if (K > 64) return cudaErrorInvalidValue;
@@ -364,11 +369,13 @@ cudaError_t launch_wino_tc64(const float *input, const float *workspace, float *
   if (e != cudaSuccess) return e;
   EncodeTiledFn enc = encode_fn();
   if (!enc) return cudaErrorNotSupported;
+  constexpr int KC = ocb::T64Cfg<DT>::kKC;
+  constexpr bool bf16 = DT == ocb::kTcBf16;
   CUtensorMap tm_in, tm_u;
   {
     cuuint64_t dims[4] = {(cuuint64_t)N, (cuuint64_t)W, (cuuint64_t)H, (cuuint64_t)C};
     cuuint64_t strides[3] = {(cuuint64_t)N * 4, (cuuint64_t)W * N * 4, (cuuint64_t)H * W * N * 4};
-    cuuint32_t box[4] = {(cuuint32_t)ocb::kTcN, 4, 4, 16};
+    cuuint32_t box[4] = {(cuuint32_t)ocb::kTcN, 4, 4, (cuuint32_t)KC};
     cuuint32_t estr[4] = {1, 1, 1, 1};
     if (enc(&tm_in, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<float *>(input), dims, strides, box, estr,
             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -376,13 +383,18 @@ cudaError_t launch_wino_tc64(const float *input, const float *workspace, float *
       return cudaErrorInvalidValue;
   }
   {
-    // workspace [C][16][K] bf16 viewed as {filter within a 128-byte row, channel, 128-byte row, position}; one row block
-    cuuint64_t dims[4] = {64, (cuuint64_t)C, (cuuint64_t)K / 64, 16};
-    cuuint64_t strides[3] = {(cuuint64_t)16 * K * 2, 128, (cuuint64_t)K * 2};
-    cuuint32_t box[4] = {64, 16, 1, 16};
+    // workspace [C][16][K] viewed as {filter within a 128-byte row, channel, 128-byte row, position}.
+    // BF16: one row block of 64 filters.  TF32: a box of four row blocks of 32 filters, of which two exist -
+    // the hardware fills the other two with zeros, which the kernel uses as the empty half of its A operand.
+    constexpr cuuint64_t esz = bf16 ? 2 : 4;
+    constexpr cuuint32_t row_elems = bf16 ? 64 : 32;
+    cuuint64_t dims[4] = {row_elems, (cuuint64_t)C, (cuuint64_t)K / row_elems, 16};
+    cuuint64_t strides[3] = {(cuuint64_t)16 * K * esz, 128, (cuuint64_t)K * esz};
+    cuuint32_t box[4] = {row_elems, (cuuint32_t)KC, bf16 ? 1u : 4u, 16};
     cuuint32_t estr[4] = {1, 1, 1, 1};
-    if (enc(&tm_u, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<float *>(workspace), dims, strides, box, estr,
-            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+    if (enc(&tm_u, bf16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4,
+            const_cast<float *>(workspace), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            bf16 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return cudaErrorInvalidValue;
   }
@@ -397,10 +409,10 @@ cudaError_t launch_wino_tc64(const float *input, const float *workspace, float *
   if (tiles > 0x7fffffffll / 8) return cudaErrorInvalidValue;
   p.total_tiles = (int)tiles;
   p.split_from = p.total_items = p.total_tiles;
-  p.chunks_per_tile = (C + 15) / 16;
+  p.chunks_per_tile = (C + KC - 1) / KC;
   p.status = st->status_ptr;
   const int grid = p.total_tiles < st->sm_count ? p.total_tiles : st->sm_count;
-  ocb::wino_tc64_kernel<<<grid, ocb::kT64Threads, ocb::kT64SmemBytes, stream>>>(tm_in, tm_u, p);
+  ocb::wino_tc64_kernel<DT><<<grid, ocb::kT64Threads, ocb::T64Cfg<DT>::kSmemBytes, stream>>>(tm_in, tm_u, p);
   return cudaGetLastError();
 }
 
@@ -415,11 +427,10 @@ cudaError_t launch_tc(const float *input, const float *workspace, float *output,
                       cudaStream_t stream, int kernel = OPENCNN_TC_AUTO) {
   if (kernel == OPENCNN_TC_SINGLE_CTA) return launch_wino_tc<DT>(input, workspace, output, N, C, H, W, K, stream);
   if (kernel == OPENCNN_TC_PAIR_LOCAL) return launch_wino_tc2<DT>(input, workspace, output, N, C, H, W, K, stream);
-  if (kernel == OPENCNN_TC_STACKED_BLOCKS)
-    return DT == ocb::kTcBf16 ? launch_wino_tc64(input, workspace, output, N, C, H, W, K, stream) : cudaErrorInvalidValue;
+  if (kernel == OPENCNN_TC_STACKED_BLOCKS) return launch_wino_tc64<DT>(input, workspace, output, N, C, H, W, K, stream);
   if (kernel != OPENCNN_TC_AUTO) return cudaErrorInvalidValue;
-  // at most 64 filters and more than one 32-image block: two blocks share the accumulator rows (BF16 only)
-  if (DT == ocb::kTcBf16 && K <= 64 && N > ocb::kTcN) return launch_wino_tc64(input, workspace, output, N, C, H, W, K, stream);
+  // at most 64 filters and more than one 32-image block: two blocks share the accumulator rows
+  if (K <= 64 && N > ocb::kTcN) return launch_wino_tc64<DT>(input, workspace, output, N, C, H, W, K, stream);
   const int k_steps = (C + ocb::TcCfg<DT>::kKC - 1) / ocb::TcCfg<DT>::kKC;
   const bool pair = DT == ocb::kTcTf32 && k_steps >= 64 && N >= 64;
   return pair ? launch_wino_tc2<DT>(input, workspace, output, N, C, H, W, K, stream)

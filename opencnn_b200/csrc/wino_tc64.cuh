@@ -1,5 +1,5 @@
-// Tensor-core Winograd kernel for layers with at most 64 filters (BF16 operands): two 32-image
-// blocks share the 128 accumulator rows of one CTA.
+// Tensor-core Winograd kernel for layers with at most 64 filters (BF16 or TF32 operands): two
+// 32-image blocks share the 128 accumulator rows of one CTA.
 //
 // Same operator as wino_tc.cuh (it replaces the reference's Winograd_kernel,
 // src/convolutionForward_32x64x8.cu:169-262, with the contraction on the tensor cores; the reference
@@ -18,6 +18,14 @@
 // layers with few channels - are paid once per 64 images, with all 128 TMEM lanes doing useful
 // work in the epilogue.  The tensor pipe does twice the MMAs per image, which it has room for.
 //
+// TF32: the A operand of an MMA is four blocks of 32 filter rows at one fixed distance, which is the
+// distance of U's own two blocks (1 KB), so the zero half has to lie right behind (resp. before)
+// them.  It does: the filter slice is loaded as a box of 128 filters of which only 64 exist, and TMA
+// fills the other half of every position (2 KB) with zeros.  [U ; 0] starts at a position's U,
+// [0 ; U] 2 KB earlier, in the zero half of the position before (position 0 of the first stage
+// has a region of zeros of its own below it; position 0 of the second stage finds the zero half of
+// the first stage's last position there, which every reload rewrites with the same zeros).
+//
 // The pipeline runs in sub-steps: (K-step, image block).  Raw patches and V have rings of three
 // sub-steps, U a ring of two K-steps.  Warp roles as in wino_tc.cuh (512 threads): warp 0 loads
 // raw patches, warp 14 loads U, warps 1-4 transform, warps 5 and 15 issue the MMAs of eight
@@ -29,26 +37,34 @@
 namespace ocb {
 
 constexpr int kT64RawStages = 3, kT64UStages = 2, kT64VStages = 3;
-constexpr uint32_t kT64RawBytes = 16 * 16 * kTcN * 4;      // [16 c][4 h][4 w][32 n] fp32: one image block, one K-step
-constexpr uint32_t kT64UBytes = 16 * 2048;                 // [16 xi][16 c][64 filters] bf16
-constexpr uint32_t kT64ZeroBytes = 2048;                   // one A block (64 filter rows x 16 channels) of zeros
+constexpr uint32_t kT64ZeroBytes = 2048;                   // one empty half of an A operand (64 filter rows x one K-step)
 constexpr int kT64Threads = 512;
-constexpr size_t kT64SmemBytes = 2 * kT64ZeroBytes + (size_t)kT64RawStages * kT64RawBytes + (size_t)kT64UStages * kT64UBytes +
-                                 (size_t)kT64VStages * kTcVBytes + 1024;
-static_assert(kT64SmemBytes <= 232448, "shared memory");
+template <int DT> struct T64Cfg {
+  static constexpr int kKC = DT == kTcBf16 ? 16 : 8;                       // channels per K-step
+  static constexpr uint32_t kRawBytes = kKC * 16 * kTcN * 4;               // [c][4 h][4 w][32 n] fp32: one image block, one K-step
+  static constexpr uint32_t kUPosBytes = DT == kTcBf16 ? 2048 : 4096;      // one position of a U stage (TF32: half of it zeros)
+  static constexpr uint32_t kUBytes = 16 * kUPosBytes;
+  // BF16 keeps a second region of zeros above the rings ([U ; 0]); TF32 needs only the one below the U ring.
+  static constexpr size_t kSmemBytes = (DT == kTcBf16 ? 2 : 1) * kT64ZeroBytes + (size_t)kT64RawStages * kRawBytes +
+                                       (size_t)kT64UStages * kUBytes + (size_t)kT64VStages * kTcVBytes + 512;
+  static_assert(kSmemBytes <= 232448, "shared memory");
+};
 
 // p.n_blocks counts 32-image blocks; p.total_tiles counts 64-image tiles; p.k_blocks is 1.
+template <int DT>
 __global__ void __launch_bounds__(kT64Threads, 1)
 wino_tc64_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant__ CUtensorMap tm_u, const WinoParams p) {
+  using Cfg = T64Cfg<DT>;
   constexpr int SR = kT64RawStages, SU = kT64UStages, SV = kT64VStages;
-  constexpr int KC = 16;
+  constexpr int KC = Cfg::kKC;
+  constexpr uint32_t kT64RawBytes = Cfg::kRawBytes, kT64UBytes = Cfg::kUBytes;
   extern __shared__ __align__(1024) uint8_t tsmem64[];
-  uint8_t *zero_lo = tsmem64;                                          // below every U stage
-  uint8_t *raw_s = zero_lo + kT64ZeroBytes;
-  uint8_t *u_s = raw_s + SR * kT64RawBytes;
+  uint8_t *raw_s = tsmem64;
+  uint8_t *zero_lo = raw_s + SR * kT64RawBytes;                        // directly below the U ring
+  uint8_t *u_s = zero_lo + kT64ZeroBytes;
   uint8_t *v_s = u_s + SU * kT64UBytes;
-  uint8_t *zero_hi = v_s + SV * kTcVBytes;                             // above every U stage
-  uint64_t *bars = reinterpret_cast<uint64_t *>(zero_hi + kT64ZeroBytes);
+  uint8_t *zero_hi = v_s + SV * kTcVBytes;                             // above every U stage (BF16 only)
+  uint64_t *bars = reinterpret_cast<uint64_t *>(zero_hi + (DT == kTcBf16 ? kT64ZeroBytes : 0));
   uint64_t *raw_full = bars, *raw_empty = raw_full + SR, *u_full = raw_empty + SR, *u_empty = u_full + SU,
            *v_ready = u_empty + SU, *v_empty = v_ready + SV;
   uint64_t *acc_full = v_empty + SV, *mma_done = acc_full + 2;   // mma_done[2]
@@ -66,7 +82,7 @@ wino_tc64_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constan
   // the two regions of zeros that stand in for the empty half of the A operand
   for (int i = tid; i < (int)(kT64ZeroBytes / 4); i += kT64Threads) {
     reinterpret_cast<uint32_t *>(zero_lo)[i] = 0u;
-    reinterpret_cast<uint32_t *>(zero_hi)[i] = 0u;
+    if (DT == kTcBf16) reinterpret_cast<uint32_t *>(zero_hi)[i] = 0u;
   }
   fence_proxy_async_smem();                                            // read by the tensor core through the async proxy
   if (tid == 0) {
@@ -133,13 +149,16 @@ wino_tc64_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constan
     }
   } else if (warp <= kTcTransformWarps) {
     // ===================================== input transform =====================================
-    const int t = tid - 32;                                            // 0..127: channel t >> 4 (and + 8), image pair t & 15
+    const int t = tid - 32;                                            // 0..127: channel t >> 4 (BF16: and + 8), image pair t & 15
     for (int g = 0; g < total_sub; ++g) {
       const int sv = g % SV, sr = g % SR;
       const uint32_t use = g / SV;
       mbar_wait(smem_u32(raw_full + sr), (g / SR) & 1, dead, p.status);
       if (use > 0) mbar_wait(smem_u32(v_empty + sv), (use - 1) & 1, dead, p.status);   // V stage free again
-      transform_to_v_bf16_x2(reinterpret_cast<const float *>(raw_s + sr * kT64RawBytes), v_s + sv * kTcVBytes, t >> 4, t & 15);
+      if (DT == kTcBf16)
+        transform_to_v_bf16_x2(reinterpret_cast<const float *>(raw_s + sr * kT64RawBytes), v_s + sv * kTcVBytes, t >> 4, t & 15);
+      else
+        transform_to_v_tf32_pair(reinterpret_cast<const float *>(raw_s + sr * kT64RawBytes), v_s + sv * kTcVBytes, t >> 4, t & 15);
       fence_proxy_async_smem();          // V is read by the tensor core through the async proxy
       __syncwarp();
       if (lane == 0) {
@@ -152,18 +171,26 @@ wino_tc64_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constan
     if (lane == 0) {
       const int me = warp == kTcMmaWarp ? 0 : 1;
       const int col0 = 2 * me;                         // columns col0, col0 + 1 of the 4x4 positions, column by column
-      const uint32_t idesc = instr_desc<kTcBf16>();
-      // A blocks: 64 filters x 16 channels, filter-contiguous rows of 128 B (128-byte swizzle), 8-channel groups 1 KB
-      // apart; the second block lies `lbo` bytes after the first.  Per position the U block moves by 2 KB, so
+      const uint32_t idesc = instr_desc<DT>();
+      // BF16.  A blocks: 64 filters x 16 channels, filter-contiguous rows of 128 B (128-byte swizzle), 8-channel
+      // groups 1 KB apart; the second block lies `lbo` bytes after the first.  Per position the U block moves by
+      // 2 KB, so
       //   [U ; 0]: start at U, second block at zero_hi  -> start + 2 KB, lbo - 2 KB per position
       //   [0 ; U]: start at zero_lo, second block at U  -> lbo + 2 KB per position
       // B: 32 images x 16 channels per position, rows of 64 B (64-byte swizzle), 8-channel groups 512 B apart.
+      // TF32.  A blocks: 32 filters x 8 channels, rows of 128 B (128-byte swizzle with 32-byte atoms), 4-channel
+      // groups 512 B apart, four blocks 1 KB apart: U, U, zeros, zeros from a position's start, and the other way
+      // round from 2 KB earlier; 4 KB per position either way.  B: rows of 128 B, blocks 1 KB apart.
       const uint32_t u0 = smem_u32(u_s);
-      const uint64_t a_top0 = smem_desc(u0, smem_u32(zero_hi) - u0, 1024, 2);
-      const uint64_t a_bot0 = smem_desc(smem_u32(zero_lo), u0 - smem_u32(zero_lo), 1024, 2);
-      constexpr uint64_t kPosStart = 2048 >> 4, kPosLbo = (uint64_t)(2048 >> 4) << 16;
+      const uint64_t a_top0 = DT == kTcBf16 ? smem_desc(u0, smem_u32(zero_hi) - u0, 1024, 2) : smem_desc(u0, 1024, 512, 1);
+      const uint64_t a_bot0 = DT == kTcBf16 ? smem_desc(smem_u32(zero_lo), u0 - smem_u32(zero_lo), 1024, 2)
+                                            : smem_desc(u0 - kT64ZeroBytes, 1024, 512, 1);
+      constexpr uint64_t kPosStart = Cfg::kUPosBytes >> 4, kPosLbo = (uint64_t)(2048 >> 4) << 16;
       constexpr uint64_t kStageStart = kT64UBytes >> 4, kStageLbo = (uint64_t)(kT64UBytes >> 4) << 16;
-      const uint64_t b_desc0 = smem_desc(smem_u32(v_s), 512, 512, 4);
+      // what a position / a stage adds to the descriptor of [U ; 0] and of [0 ; U]
+      constexpr uint64_t kTopPos = DT == kTcBf16 ? kPosStart - kPosLbo : kPosStart, kBotPos = DT == kTcBf16 ? kPosLbo : kPosStart;
+      constexpr uint64_t kTopStage = DT == kTcBf16 ? kStageStart - kStageLbo : kStageStart, kBotStage = DT == kTcBf16 ? kStageLbo : kStageStart;
+      const uint64_t b_desc0 = DT == kTcBf16 ? smem_desc(smem_u32(v_s), 512, 512, 4) : smem_desc(smem_u32(v_s), 1024, 512, 1);
       int ci = 0, seq = 0;
       for (int g = 0; g < total_sub; ++g) {
         const int b = g & 1, su = (g >> 1) % SU, sv = g % SV;
@@ -171,8 +198,8 @@ wino_tc64_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constan
         if (b == 0 && !mbar_wait(smem_u32(u_full + su), ((g >> 1) / SU) & 1, dead, p.status)) break;
         if (!mbar_wait(smem_u32(v_ready + sv), (g / SV) & 1, dead, p.status)) break;
         tc_fence_after();
-        const uint64_t astep = b == 0 ? kPosStart - kPosLbo : kPosLbo;
-        const uint64_t ad = (b == 0 ? a_top0 + (uint64_t)su * (kStageStart - kStageLbo) : a_bot0 + (uint64_t)su * kStageLbo) + (uint64_t)col0 * astep;
+        const uint64_t astep = b == 0 ? kTopPos : kBotPos;
+        const uint64_t ad = (b == 0 ? a_top0 + (uint64_t)su * kTopStage : a_bot0 + (uint64_t)su * kBotStage) + (uint64_t)col0 * astep;
         const uint64_t bd = b_desc0 + (uint64_t)(sv * (kTcVBytes >> 4)) + (uint64_t)(col0 * (1024 >> 4));
         const uint32_t accumulate = (ci > 0 || b > 0) ? 1u : 0u, d0 = tmem_base + col0 * kTcN;
         bool ok = true;
@@ -183,7 +210,7 @@ wino_tc64_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constan
             if (!mbar_wait(smem_u32(acc_empty + col0 + (xo >> 2)), (seq - 1) & 1, dead, p.status)) { ok = false; break; }
             tc_fence_after();
           }
-          tc_mma<kTcBf16>(d0 + xr * kTcN, ad + (uint64_t)xr * astep, bd + (uint64_t)(xr * (1024 >> 4)), idesc, accumulate);
+          tc_mma<DT>(d0 + xr * kTcN, ad + (uint64_t)xr * astep, bd + (uint64_t)(xr * (1024 >> 4)), idesc, accumulate);
         }
         if (!ok) break;
         tc_commit(smem_u32(v_empty + sv));                 // V stage reusable when these MMAs are done

@@ -175,33 +175,39 @@ def test_each_tensor_core_kernel(oracle, libs, precision, kernel):
     assert api.winograd_forward_kernel(bad, bad, bad, 32, 8, 4, 4, 64, precision="fp32", kernel=kernel) != 0
 
 
-# The stacked-blocks kernel (BF16, at most 64 filters): even and odd numbers of 32-image blocks, a ragged last
-# block, channel counts that are not a multiple of the K-step, one K-step and many.
+# The stacked-blocks kernel (at most 64 filters): even and odd numbers of 32-image blocks, a ragged last block,
+# channel counts that are not a multiple of the K-step, one K-step and many, more tiles than SMs (so that both
+# stages of the filter ring are reused).
 STACKED_SHAPES = [(64, 16, 64, 8, 8), (96, 40, 64, 5, 9), (128, 64, 64, 14, 14), (72, 3, 64, 6, 6), (32, 32, 64, 7, 7),
-                  (200, 72, 64, 3, 5), (256, 32, 64, 12, 12)]
+                  (200, 72, 64, 3, 5), (256, 32, 64, 12, 12), (256, 32, 64, 30, 30)]
 
 
-def test_stacked_blocks_kernel(oracle, libs):
+@pytest.mark.parametrize("precision", ["tf32", "bf16"])
+def test_stacked_blocks_kernel(oracle, libs, precision):
+    rnd = oracle.round_tf32 if precision == "tf32" else oracle.round_bf16
     for (N, C, K, H, W) in STACKED_SHAPES:
-        x = oracle.round_bf16(oracle.input_chwn(N, C, H, W)).reshape(C, H, W, N)
-        g = oracle.round_bf16(oracle.filter_crsk(C, K)).reshape(C, 3, 3, K)
+        x = rnd(oracle.input_chwn(N, C, H, W)).reshape(C, H, W, N)
+        g = rnd(oracle.filter_crsk(C, K)).reshape(C, 3, 3, K)
         dx, dg = torch.from_numpy(x).cuda(), torch.from_numpy(g).cuda()
         dws = torch.empty((C, 4, 4, K), device="cuda")
-        assert api.filter_transform(dg, dws, C, K, precision="bf16") == 0
+        assert api.filter_transform(dg, dws, C, K, precision=precision) == 0
         outs = []
         for _ in range(2):
             dy = torch.full((K, H, W, N), float("nan"), device="cuda")
-            assert api.winograd_forward_kernel(dx, dws, dy, N, C, H, W, K, precision="bf16", kernel="stacked") == 0
+            assert api.winograd_forward_kernel(dx, dws, dy, N, C, H, W, K, precision=precision, kernel="stacked") == 0
             assert api.last_device_status() == 0, (N, C, K, H, W)
             outs.append(dy)
         assert torch.equal(outs[0], outs[1]), "not repeatable"
+        # the single-CTA kernel issues the same products in the same order: the two must agree bit for bit
+        single = torch.full((K, H, W, N), float("nan"), device="cuda")
+        assert api.winograd_forward_kernel(dx, dws, single, N, C, H, W, K, precision=precision, kernel="single") == 0
+        assert torch.equal(outs[0], single), (N, C, K, H, W)
         y = outs[0].cpu().numpy()
         assert np.isfinite(y).all(), (N, C, K, H, W)
-        model = oracle.tc_model(x, g, "bf16")
+        model = oracle.tc_model(x, g, precision)
         rms = float(np.sqrt(np.mean(model.astype(np.float64) ** 2)))
         worst = float(np.abs(y - model).max())
         assert worst <= MODEL_REL * max(rms, 1e-30), f"{(N, C, K, H, W)}: {worst / rms:.3e} of rms"
-    # refused: more than 64 filters, TF32
+    # refused: more than 64 filters
     z = torch.zeros(1 << 16, device="cuda")
-    assert api.winograd_forward_kernel(z, z, z, 64, 16, 4, 4, 128, precision="bf16", kernel="stacked") != 0
-    assert api.winograd_forward_kernel(z, z, z, 64, 16, 4, 4, 64, precision="tf32", kernel="stacked") != 0
+    assert api.winograd_forward_kernel(z, z, z, 64, 16, 4, 4, 128, precision=precision, kernel="stacked") != 0
