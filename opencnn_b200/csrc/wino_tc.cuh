@@ -13,17 +13,18 @@
 // Both operands are "MN-major" in shared memory (M resp. N contiguous), which is how they exist
 // anyway: U rows of consecutive filters come straight from the transformed-filter workspace by
 // TMA (128-byte swizzle), V rows of consecutive images are written by the transform threads.
-// Per K-step (16 channels in BF16, 8 in TF32) 16 MMAs are issued, by two threads in BF16 and four in TF32.
+// Per K-step (16 channels in BF16, 8 in TF32) 16 MMAs are issued, by two threads.
 //
-// Warp roles (512 threads in BF16, 576 in TF32):
+// Warp roles (512 threads):
 //   warp 0      TMA: raw input patches (4-D box, hardware zero-fill = halo), a ring of their own
 //   warp 14     TMA: U slices (a loader of its own, so patches never queue behind filter slices)
 //   warps 1-4   input transform B^T d B in fp32, rounding, V written in the UMMA layout
-//   warps 5,15+ MMA issue (one thread each, 8 or 4 positions per thread), tcgen05.commit to free stages
+//   warps 5,15  MMA issue (one thread each, 8 positions per thread), tcgen05.commit to free stages
 //               and to publish a finished tile; warp 5 also owns the TMEM allocation
 //   warps 6-13  epilogue, two warps per TMEM lane quarter (each takes half of the 32 images):
-//               tcgen05.ld the 16 positions of (filter = TMEM lane, 4 images), A^T M A in
-//               registers - no shared-memory transpose - 32-byte stores
+//               tcgen05.ld one column of the 4x4 positions of (filter = TMEM lane, 8 images) at a
+//               time, A^T M A accumulated in registers - no shared-memory transpose - neighbouring
+//               lanes swap image halves, 32-byte stores in 64-byte runs
 // All hand-offs are mbarriers with bounded waits.
 #pragma once
 #include "fx.cuh"
@@ -61,10 +62,11 @@ template <int DT, bool HU = false> struct TcCfg {
   static constexpr int kRawStages = (DT == kTcBf16 && !HU) ? 2 : 4;
   static constexpr uint32_t kUPosBytes = HU ? 2048 : 4096;           // one position of a U stage
   static constexpr uint32_t kUBytes = 16 * kUPosBytes;
-  // MMA-issuing threads (warp kTcMmaWarp and warps kTcMmaWarpB ..).  TF32 has twice the MMAs per
-  // channel, and its transform threads are cheap enough for four issuers to pay (3-5 %); in BF16
-  // four measured the same as two.
-  static constexpr int kIssuers = DT == kTcBf16 ? 2 : 4;
+  // MMA-issuing threads (warp kTcMmaWarp and warps kTcMmaWarpB ..).  Two: one thread cannot issue
+  // these small MMAs faster than one per ~52 cycles, two keep the tensor pipe fed (40 cycles per
+  // MMA).  Four measured the same as two in BF16; in TF32 they cost more than they bring, because
+  // 18 warps leave the epilogue 96 registers per thread instead of 128 (3-7 % slower).
+  static constexpr int kIssuers = 2;
   static constexpr int kThreads = (kTcMmaWarpB + kIssuers - 1) * 32;
   static constexpr size_t kSmemBytes = (size_t)kRawStages * kRawBytes + (size_t)kTcStages * (kUBytes + kTcVBytes) + 1024;
 };
@@ -363,7 +365,7 @@ wino_tc_kernel(const __grid_constant__ CUtensorMap tm_in, const __grid_constant_
     // loop: building them per instruction made each of these small MMAs (N = 32 occupies the
     // tensor pipe ~50 cycles) cost ~180 cycles.
     if (lane == 0) {
-      // A thread issues whole columns of the 4x4 positions (two columns in BF16, one in TF32), column by column:
+      // A thread issues whole columns of the 4x4 positions (two columns each), column by column:
       // the epilogue hands the accumulators back per column, so the next tile's first MMAs start while the
       // other columns are still being read.
       constexpr int kPer = 16 / Cfg::kIssuers;                              // positions per issuing thread
