@@ -38,7 +38,8 @@ enum TcType : int { kTcBf16 = 0, kTcTf32 = 1 };
 constexpr int kTcEpilogueWarps = 8;
 // Four transform warps, two items per thread and K-step.  Eight warps with one item each were
 // measured too: the CTA then has 640 threads, the register cap drops to 96 and the epilogue
-// spills - 3-5 % slower.  Two groups of two warps taking K-steps alternately were 8 % slower
+// spills - 3-5 % slower; eight transform warps with four epilogue warps (two passes each), which
+// keeps 512 threads, were 2-5 % slower too.  Two groups of two warps taking K-steps alternately were 8 % slower
 // (the transform's latency per K-step matters, not only its throughput).
 constexpr int kTcTransformWarps = 4;                          // warps 1 .. kTcTransformWarps
 constexpr int kTcMmaWarp = 1 + kTcTransformWarps;             // first MMA-issuing thread (also owns the TMEM allocation)
