@@ -1,5 +1,5 @@
 // Thin wrappers over the sm_100a PTX this library uses: mbarrier (with bounded waits), TMA
-// tiled loads (never multicast), proxy fences and the packed fp32 FMA.
+// tiled loads (each into one CTA), proxy fences and the packed fp32 FMA.
 #pragma once
 #include <cuda.h>
 #include <cuda_runtime.h>
