@@ -575,7 +575,7 @@ def main():
             tf_fused = sum(r_["fused_us"] for r_ in rows) * 1e-6
             pk = peaks["bf16_tflops"] if prec == "bf16" else peaks["tf32_tflops"]
             tensor_core[prec] = {"layers": rows, "eff_tflops": td / (tt * 1e-3) * 1e-12, "ms_per_step": tt,
-                                 "roofline": {"bound": "tensor", "kernel": "wino_tc_kernel", "achieved": tg / tf_fused * 1e-12,
+                                 "roofline": {"bound": "tensor", "kernel": "wino_tc_kernel (wino_tc64_kernel on the 64-filter layer: the library's own dispatch)", "achieved": tg / tf_fused * 1e-12,
                                               "peak": pk, "unit": "TFLOP/s", "frac": tg / tf_fused * 1e-12 / pk}}
             if accuracy and prec in accuracy:
                 tensor_core[prec]["max_err_over_rms"] = accuracy[prec]["max_err_over_rms"]
