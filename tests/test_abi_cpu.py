@@ -24,6 +24,19 @@ def test_header_lists_the_expected_entry_points():
     assert set(names) == set(_lib.SIGNATURES), (names, sorted(_lib.SIGNATURES))
 
 
+def test_python_enums_match_the_header():
+    """The precision and tensor-core kernel codes of the Python mirror are the header's enumerators."""
+    text = open(os.path.join(ROOT, "include", "opencnn_b200.h")).read()
+    enums = {m.group(1): int(m.group(2)) for m in re.finditer(r"\b(OPENCNN_[A-Z0-9_]+)\s*=\s*(\d+)", text)}
+    assert enums["OPENCNN_FP32"] == api.PRECISIONS["fp32"] and enums["OPENCNN_TF32"] == api.PRECISIONS["tf32"]
+    assert enums["OPENCNN_BF16"] == api.PRECISIONS["bf16"]
+    header_kernels = {"auto": "OPENCNN_TC_AUTO", "single": "OPENCNN_TC_SINGLE_CTA", "pair_local": "OPENCNN_TC_PAIR_LOCAL",
+                      "stacked": "OPENCNN_TC_STACKED_BLOCKS"}
+    assert set(api.TC_KERNELS) == set(header_kernels)
+    for name, enumerator in header_kernels.items():
+        assert api.TC_KERNELS[name] == enums[enumerator], name
+
+
 @pytest.mark.parametrize("variant", build.VARIANTS)
 def test_library_exports_every_declared_symbol(libs, variant):
     lib = libs[variant]
